@@ -1,0 +1,564 @@
+// The Ulysses 4D all-to-all as ONE persistent sm_100a kernel: opening handshake, payload pushed to
+// every peer's window at its permuted offset, closing handshake, and (optionally) the copy-out of
+// the own window into a caller-owned tensor. The relayout is expressed in the addresses of the
+// copies, so there is no permute pass.
+//
+// Parity with the reference: replaces src/barrier.cu:31-49 (two one-block barrier launches),
+// src/transfer.cu:68-126 (one cudaMemcpy2D/3DAsync per peer on the copy engines) and
+// src/bindings.cc:216-223 (the flat copy-out) with a single launch whose data plane is SM-issued
+// bulk (TMA) copies: local global -> shared -> the peer's window over NVLink, all peers in flight
+// at once. Ordering rests on the PTX memory model only: payload copies complete, fence.acq_rel.sys,
+// CTA arrival counter, then red.release.sys on the peer's flag; the reader spins with
+// ld.acquire.sys. Every spin is bounded and reports through the control block's status words.
+#include "fu_kernels.h"
+#include "host_util.h"
+#include "ptx.cuh"
+
+#include <algorithm>
+
+static_assert(sizeof(FuCtrl) == FU_CTRL_BYTES, "control block layout");
+
+namespace {
+
+using namespace fu::ptx;
+
+constexpr int      kStages      = 4;
+constexpr int      kStageBytes  = 48 * 1024;
+constexpr int      kAhead       = kStages - 2;  // loads issued this many chunks ahead of the stores
+constexpr int      kLdstThreads = 512;
+constexpr int      kDefaultCtas = 32;
+constexpr uint32_t kDefaultTimeoutMs = 10000;
+
+// A route plus its decomposition into chunks of at most one stage.
+struct RouteX {
+    const uint8_t* src;
+    uint8_t*       dst;
+    int64_t        src_pitch, dst_pitch, src_batch, dst_batch;
+    int64_t        rows, batches;
+    int64_t        row_bytes;
+    int64_t        piece_bytes;     // bytes of a row moved by one chunk when a row exceeds a stage
+    int32_t        pieces_per_row;  // > 1 only when rows_per_chunk == 1
+    int32_t        rows_per_chunk;
+    int64_t        row_groups;      // ceil(rows / rows_per_chunk)
+    int64_t        count;           // chunks in this route
+};
+
+struct RouteSet {
+    int     n;
+    int64_t max_count;
+    RouteX  r[FU_MAX_WORLD];
+};
+
+struct KArgs {
+    RouteSet push;
+    RouteSet copy_out;  // n == 0 when there is no fused copy-out
+    FuCtrl*  own;
+    FuCtrl*  peer_ctrl[FU_MAX_WORLD];
+    int      rank, world, flags;
+    uint64_t timeout_ns;
+};
+
+struct Chunk {
+    const uint8_t* src;
+    uint8_t*       dst;
+    int64_t        src_pitch, dst_pitch;
+    uint32_t       nrows, row_bytes;
+};
+
+// Round-robin over routes: virtual index v names (route v % n, chunk v / n); a route that has run
+// out of chunks yields nothing for that v. With gridDim a multiple of n each CTA streams to one peer.
+struct ChunkCursor {
+    int64_t v, stride, end;
+    __device__ ChunkCursor(const RouteSet& s, int cta, int ctas) : v(cta), stride(ctas), end(s.max_count * s.n) {}
+    __device__ bool next(const RouteSet& s, Chunk& c)
+    {
+        while (v < end) {
+            const int     ri  = static_cast<int>(v % s.n);
+            const int64_t idx = v / s.n;
+            v += stride;
+            const RouteX& r = s.r[ri];
+            if (idx >= r.count) {
+                continue;
+            }
+            const int64_t per_batch = r.row_groups * r.pieces_per_row;
+            const int64_t batch     = idx / per_batch;
+            const int64_t rem       = idx - batch * per_batch;
+            const int64_t group     = rem / r.pieces_per_row;
+            const int64_t piece     = rem - group * r.pieces_per_row;
+            const int64_t row0      = group * r.rows_per_chunk;
+            const int64_t col0      = piece * r.piece_bytes;
+            c.nrows     = static_cast<uint32_t>(min(static_cast<int64_t>(r.rows_per_chunk), r.rows - row0));
+            c.row_bytes = static_cast<uint32_t>(min(r.piece_bytes, r.row_bytes - col0));
+            c.src       = r.src + batch * r.src_batch + row0 * r.src_pitch + col0;
+            c.dst       = r.dst + batch * r.dst_batch + row0 * r.dst_pitch + col0;
+            c.src_pitch = r.src_pitch;
+            c.dst_pitch = r.dst_pitch;
+            return true;
+        }
+        return false;
+    }
+};
+
+__device__ void report(FuCtrl* own, uint32_t code, uint32_t peer, uint64_t expected, uint64_t seen)
+{
+    if (atomicCAS(&own->status[0], 0u, code) == 0u) {
+        own->status[1] = peer;
+        own->status[2] = static_cast<uint32_t>(expected);
+        own->status[3] = static_cast<uint32_t>(expected >> 32);
+        own->status[4] = static_cast<uint32_t>(seen);
+        own->status[5] = static_cast<uint32_t>(seen >> 32);
+    }
+}
+
+// Called by one full warp. Lane p < world announces `value` to rank p.
+__device__ void announce(const KArgs& a, uint64_t value)
+{
+    const int lane = threadIdx.x & 31;
+    if (lane < a.world && !(a.flags & FU_A2A_MUTE)) {
+        red_release_sys_max(&a.peer_ctrl[lane]->flags[a.rank], value);
+    }
+}
+
+// Called by one full warp. Lane p < world waits until rank p has announced at least `target`.
+// Returns false (on every lane) after the time limit, having recorded who was missing.
+__device__ bool await(const KArgs& a, uint64_t target, uint32_t code)
+{
+    const int lane = threadIdx.x & 31;
+    bool      ok   = true;
+    if (lane < a.world) {
+        const uint64_t t0    = globaltimer_ns();
+        uint32_t       spins = 0;
+        uint64_t       seen;
+        while ((seen = ld_acquire_sys(&a.own->flags[lane])) < target) {
+            ++spins;
+            if ((spins & 63u) == 0u) {
+                if (globaltimer_ns() - t0 > a.timeout_ns || spins > 0x7fffff00u) {
+                    report(a.own, code, static_cast<uint32_t>(lane), target, seen);
+                    ok = false;
+                    break;
+                }
+                __nanosleep(64);
+            }
+        }
+    }
+    return __all_sync(0xffffffffu, ok);
+}
+
+// ---- data movers ------------------------------------------------------------------------------------
+struct BulkPipe {
+    uint8_t*  stage[kStages];
+    uint64_t* full;  // kStages mbarriers
+};
+
+__device__ __forceinline__ void bulk_issue_loads(const BulkPipe& p, int s, const Chunk& c, int lane)
+{
+    const uint32_t total = c.nrows * c.row_bytes;
+    if (lane == 0) {
+        mbar_expect_tx(&p.full[s], total);
+    }
+    __syncwarp();
+    if (c.src_pitch == c.row_bytes) {
+        if (lane == 0) {
+            bulk_g2s(p.stage[s], c.src, total, &p.full[s]);
+        }
+    }
+    else {
+        for (uint32_t r = lane; r < c.nrows; r += 32) {
+            bulk_g2s(p.stage[s] + r * c.row_bytes, c.src + r * c.src_pitch, c.row_bytes, &p.full[s]);
+        }
+    }
+}
+
+__device__ __forceinline__ void bulk_issue_stores(const BulkPipe& p, int s, const Chunk& c, int lane)
+{
+    if (c.dst_pitch == c.row_bytes) {
+        if (lane == 0) {
+            bulk_s2g(c.dst, p.stage[s], c.nrows * c.row_bytes);
+        }
+    }
+    else {
+        for (uint32_t r = lane; r < c.nrows; r += 32) {
+            bulk_s2g(c.dst + r * c.dst_pitch, p.stage[s] + r * c.row_bytes, c.row_bytes);
+        }
+    }
+    bulk_commit();  // every lane commits one (possibly empty) group per chunk
+}
+
+// Moves this CTA's share of a route set with one warp. `jbase` continues the stage/parity sequence
+// across successive calls in one kernel. Returns false if a load never completed.
+__device__ bool bulk_move(const RouteSet& set, const BulkPipe& p, int64_t& jbase, FuCtrl* own)
+{
+    const int   lane = threadIdx.x & 31;
+    ChunkCursor load_cur(set, blockIdx.x, gridDim.x);
+    ChunkCursor store_cur(set, blockIdx.x, gridDim.x);
+    Chunk       c;
+    int64_t     jl = jbase;  // next chunk number to load
+    int64_t     js = jbase;  // next chunk number to store
+    bool        ok = true;
+    for (int q = 0; q < kAhead; ++q) {
+        if (!load_cur.next(set, c)) {
+            break;
+        }
+        // stage reuse across calls: the previous call drained every group before returning
+        bulk_issue_loads(p, static_cast<int>(jl % kStages), c, lane);
+        ++jl;
+    }
+    while (store_cur.next(set, c)) {
+        Chunk ahead;
+        if (load_cur.next(set, ahead)) {
+            // the stage about to be refilled was last read by the store issued two chunks ago
+            bulk_wait_read<1>();
+            __syncwarp();
+            bulk_issue_loads(p, static_cast<int>(jl % kStages), ahead, lane);
+            ++jl;
+        }
+        const int      s      = static_cast<int>(js % kStages);
+        const uint32_t parity = static_cast<uint32_t>((js / kStages) & 1);
+        if (!mbar_wait(&p.full[s], parity)) {
+            report(own, FU_ST_COPY_TIMEOUT, 0, static_cast<uint64_t>(js), 0);
+            ok = false;
+        }
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) {
+            break;
+        }
+        fence_proxy_async_smem();
+        bulk_issue_stores(p, s, c, lane);
+        ++js;
+    }
+    bulk_wait<0>();  // writes performed, not merely read out of shared memory
+    __syncwarp();
+    jbase = ok ? js : jl;
+    return ok;
+}
+
+// `kCoherent` selects plain loads: required when the source was written during this launch (the own
+// window, filled by peers), where the read-only path must not be used.
+template <bool kCoherent>
+__device__ void ldst_move(const RouteSet& set)
+{
+    ChunkCursor cur(set, blockIdx.x, gridDim.x);
+    Chunk       c;
+    while (cur.next(set, c)) {
+        const uint32_t vpr  = c.row_bytes >> 4;
+        const uint32_t nvec = vpr * c.nrows;
+        for (uint32_t v0 = threadIdx.x; v0 < nvec; v0 += 4 * blockDim.x) {
+            uint4    val[4];
+            uint8_t* dst[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const uint32_t v = v0 + u * blockDim.x;
+                if (v < nvec) {
+                    const uint32_t row = v / vpr;
+                    const uint32_t col = v - row * vpr;
+                    const uint8_t* from = c.src + row * c.src_pitch + (static_cast<int64_t>(col) << 4);
+                    val[u]             = kCoherent ? ld_v4(from) : ld_nc_v4(from);
+                    dst[u]             = c.dst + row * c.dst_pitch + (static_cast<int64_t>(col) << 4);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                if (v0 + u * blockDim.x < nvec) {
+                    st_v4(dst[u], val[u]);
+                }
+            }
+        }
+    }
+}
+
+// ---- the kernel ---------------------------------------------------------------------------------------
+template <bool kBulk>
+__global__ void __launch_bounds__(kBulk ? 32 : kLdstThreads, 1) a2a4d_kernel(const __grid_constant__ KArgs a)
+{
+    extern __shared__ __align__(1024) uint8_t smem[];
+    __shared__ uint64_t                       full_bar[kStages];
+    __shared__ uint32_t                       ticket_s;
+
+    const int  warp      = threadIdx.x >> 5;
+    const int  lane      = threadIdx.x & 31;
+    const bool handshake = !(a.flags & FU_A2A_NO_HANDSHAKE);
+    const bool stamps    = (a.flags & FU_A2A_STAMPS) && blockIdx.x == 0 && threadIdx.x == 0;
+    FuCtrl*    own       = a.own;
+
+    BulkPipe pipe;
+    if (kBulk) {
+        for (int s = 0; s < kStages; ++s) {
+            pipe.stage[s] = smem + s * kStageBytes;
+        }
+        pipe.full = full_bar;
+        if (threadIdx.x == 0) {
+            for (int s = 0; s < kStages; ++s) {
+                mbar_init(&full_bar[s], 1);
+            }
+            mbar_fence_init();
+        }
+        __syncthreads();
+    }
+
+    // Stable for the whole launch: only the last CTA to finish advances it.
+    const uint64_t base = *reinterpret_cast<volatile uint64_t*>(&own->epoch);
+    if (stamps) {
+        own->stamps[0] = globaltimer_ns();
+    }
+
+    // Opening: "writers wait for readers". Each rank announces that everything it had queued before
+    // this launch, its reads of its own window included, is finished; nobody overwrites a window
+    // before its owner said so. Every CTA polls the (local) flags itself, so there is no grid-wide
+    // dependency here.
+    bool alive = true;
+    if (handshake && warp == 0) {
+        if (blockIdx.x == 0) {
+            announce(a, base + 1);
+            if (a.flags & FU_A2A_EARLY_PUBLISH) {
+                announce(a, base + 2);
+            }
+        }
+        alive = await(a, base + 1, FU_ST_OPEN_TIMEOUT);
+    }
+    if (stamps) {
+        own->stamps[1] = globaltimer_ns();
+    }
+
+    int64_t chunk_no = 0;
+    if (kBulk) {
+        if (alive) {
+            alive = bulk_move(a.push, pipe, chunk_no, own);
+        }
+    }
+    else {
+        __syncthreads();
+        ldst_move<false>(a.push);
+    }
+    // Make this CTA's payload visible system-wide before its arrival can be observed.
+    fence_sys();
+    __syncthreads();
+    if (stamps) {
+        own->stamps[2] = globaltimer_ns();
+    }
+
+    if (threadIdx.x == 0) {
+        ticket_s = atomicAdd(&own->arrive[0], 1u);
+    }
+    __syncthreads();
+    const bool last_in = (ticket_s == gridDim.x - 1);
+    const bool copying = a.copy_out.n > 0;
+
+    // Closing: "all my writes have landed". The CTA that arrives last has, through the arrival
+    // counter and the fences around it, every other CTA's payload ordered before its announcement.
+    if (handshake && warp == 0) {
+        if (last_in) {
+            fence_sys();
+            announce(a, base + 2);
+        }
+        if (last_in || copying) {
+            await(a, base + 2, FU_ST_CLOSE_TIMEOUT);
+        }
+    }
+    if (stamps) {
+        own->stamps[3] = globaltimer_ns();
+    }
+
+    if (copying) {
+        __syncthreads();
+        if (kBulk) {
+            fence_proxy_async();  // the bulk loads below read what peers wrote through the generic proxy
+            bulk_move(a.copy_out, pipe, chunk_no, own);
+        }
+        else {
+            ldst_move<true>(a.copy_out);
+        }
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            ticket_s = atomicAdd(&own->arrive[1], 1u);
+        }
+        __syncthreads();
+    }
+    const bool last_out = copying ? (ticket_s == gridDim.x - 1) : last_in;
+    if (last_out && threadIdx.x == 0) {
+        own->arrive[0] = 0;
+        own->arrive[1] = 0;
+        if (a.flags & FU_A2A_STAMPS) {
+            own->stamps[4] = globaltimer_ns();
+        }
+        __threadfence();
+        *reinterpret_cast<volatile uint64_t*>(&own->epoch) = base + 2;
+    }
+}
+
+__global__ void __launch_bounds__(32, 1)
+    barrier_kernel(FuCtrl* own, const __grid_constant__ KArgs a)
+{
+    const uint64_t base = *reinterpret_cast<volatile uint64_t*>(&own->epoch);
+    announce(a, base + 1);
+    await(a, base + 1, FU_ST_OPEN_TIMEOUT);
+    __syncwarp();
+    if (threadIdx.x == 0) {
+        *reinterpret_cast<volatile uint64_t*>(&own->epoch) = base + 1;
+    }
+}
+
+// ---- host side ----------------------------------------------------------------------------------------
+int decompose(RouteX& x)
+{
+    if (x.row_bytes <= 0 || x.rows <= 0 || x.batches <= 0) {
+        x.count = 0;
+        return 0;
+    }
+    if (x.row_bytes <= kStageBytes) {
+        x.piece_bytes    = x.row_bytes;
+        x.pieces_per_row = 1;
+        x.rows_per_chunk = static_cast<int32_t>(std::min<int64_t>(kStageBytes / x.row_bytes, x.rows));
+    }
+    else {
+        x.piece_bytes    = kStageBytes;
+        x.pieces_per_row = static_cast<int32_t>((x.row_bytes + kStageBytes - 1) / kStageBytes);
+        x.rows_per_chunk = 1;
+    }
+    x.row_groups = (x.rows + x.rows_per_chunk - 1) / x.rows_per_chunk;
+    x.count      = x.batches * x.row_groups * x.pieces_per_row;
+    return 0;
+}
+
+bool aligned16(const void* p)
+{
+    return (reinterpret_cast<uintptr_t>(p) & 15u) == 0;
+}
+
+}  // namespace
+
+extern "C" int fu_a2a4d(const FuA2AArgs* args, void* stream_v)
+{
+    if (!args) {
+        return fu::fail(FU_E_ARG, "fu_a2a4d: null args");
+    }
+    const FuA2AArgs& in = *args;
+    if (in.world < 1 || in.world > FU_MAX_WORLD || in.rank < 0 || in.rank >= in.world) {
+        return fu::fail(FU_E_ARG, "fu_a2a4d: rank %d / world %d out of range", in.rank, in.world);
+    }
+    if (in.n_routes < 0 || in.n_routes > FU_MAX_WORLD) {
+        return fu::fail(FU_E_ARG, "fu_a2a4d: %d routes", in.n_routes);
+    }
+    KArgs k{};
+    k.rank       = in.rank;
+    k.world      = in.world;
+    k.flags      = in.flags;
+    k.timeout_ns = static_cast<uint64_t>(in.timeout_ms ? in.timeout_ms : kDefaultTimeoutMs) * 1000000ull;
+    for (int p = 0; p < in.world; ++p) {
+        if (!in.peer_win[p] || !in.peer_ctrl[p]) {
+            return fu::fail(FU_E_ARG, "fu_a2a4d: no window or control block for rank %d", p);
+        }
+        k.peer_ctrl[p] = in.peer_ctrl[p];
+    }
+    k.own = in.peer_ctrl[in.rank];
+    if (in.n_routes > 0 && !aligned16(in.src)) {
+        return fu::fail(FU_E_ARG, "fu_a2a4d: the input is not 16-byte aligned");
+    }
+    k.push.n = 0;
+    for (int i = 0; i < in.n_routes; ++i) {
+        const FuRoute& r = in.routes[i];
+        if (r.peer < 0 || r.peer >= in.world) {
+            return fu::fail(FU_E_ARG, "fu_a2a4d: route %d names rank %d", i, r.peer);
+        }
+        if ((r.row_bytes | r.src_off | r.dst_off | r.src_pitch | r.dst_pitch | r.src_batch | r.dst_batch) & 15) {
+            return fu::fail(FU_E_ARG, "fu_a2a4d: route %d is not 16-byte granular", i);
+        }
+        if (!aligned16(in.peer_win[r.peer])) {
+            return fu::fail(FU_E_ARG, "fu_a2a4d: rank %d's window is not 16-byte aligned", r.peer);
+        }
+        RouteX x{};
+        x.src       = static_cast<const uint8_t*>(in.src) + r.src_off;
+        x.dst       = static_cast<uint8_t*>(in.peer_win[r.peer]) + r.dst_off;
+        x.src_pitch = r.src_pitch;
+        x.dst_pitch = r.dst_pitch;
+        x.src_batch = r.src_batch;
+        x.dst_batch = r.dst_batch;
+        x.rows      = r.rows;
+        x.batches   = r.batches;
+        x.row_bytes = r.row_bytes;
+        decompose(x);
+        if (x.count > 0) {
+            k.push.r[k.push.n++] = x;
+            k.push.max_count     = std::max(k.push.max_count, x.count);
+        }
+    }
+    k.copy_out.n = 0;
+    if (in.out && in.out_bytes > 0) {
+        if (!aligned16(in.out) || (in.out_bytes & 15)) {
+            return fu::fail(FU_E_ARG, "fu_a2a4d: the copy-out destination is not 16-byte granular");
+        }
+        const int64_t whole = in.out_bytes / kStageBytes;
+        const int64_t tail  = in.out_bytes - whole * kStageBytes;
+        auto flat = [&](int64_t off, int64_t row_bytes, int64_t rows) {
+            RouteX x{};
+            x.src       = static_cast<const uint8_t*>(in.peer_win[in.rank]) + off;
+            x.dst       = static_cast<uint8_t*>(in.out) + off;
+            x.src_pitch = x.dst_pitch = row_bytes;
+            x.rows      = rows;
+            x.batches   = 1;
+            x.row_bytes = row_bytes;
+            decompose(x);
+            // one stage-sized chunk per row keeps every CTA's chunks far apart in memory
+            x.rows_per_chunk = 1;
+            x.row_groups     = rows;
+            x.count          = rows;
+            k.copy_out.r[k.copy_out.n++] = x;
+            k.copy_out.max_count         = std::max(k.copy_out.max_count, x.count);
+        };
+        if (whole > 0) {
+            flat(0, kStageBytes, whole);
+        }
+        if (tail > 0) {
+            flat(whole * kStageBytes, tail, 1);
+        }
+    }
+
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    int          ctas   = in.ctas > 0 ? in.ctas : kDefaultCtas;
+    int          dev = 0, sms = 0;
+    FU_CUDA_OK(cudaGetDevice(&dev));
+    FU_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    // Every CTA must be resident at once: CTAs wait on one another's arrival counters.
+    ctas = std::max(1, std::min(ctas, sms));
+    if (k.push.n > 1 && ctas > k.push.n) {
+        ctas -= ctas % k.push.n;  // a multiple of the route count pins each CTA to one peer
+    }
+    if (in.flags & FU_A2A_LDST) {
+        a2a4d_kernel<false><<<ctas, kLdstThreads, 0, stream>>>(k);
+    }
+    else {
+        static bool configured[64] = {};
+        const int   smem_bytes     = kStages * kStageBytes;
+        if (dev < 64 && !configured[dev]) {
+            FU_CUDA_OK(cudaFuncSetAttribute(a2a4d_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                            smem_bytes));
+            configured[dev] = true;
+        }
+        a2a4d_kernel<true><<<ctas, 32, smem_bytes, stream>>>(k);
+    }
+    FU_CUDA_OK(cudaGetLastError());
+    return FU_OK;
+}
+
+extern "C" int fu_barrier(FuCtrl* const* peer_ctrl, int rank, int world, uint32_t timeout_ms, int flags,
+                          void* stream_v)
+{
+    if (world < 1 || world > FU_MAX_WORLD || rank < 0 || rank >= world || !peer_ctrl) {
+        return fu::fail(FU_E_ARG, "fu_barrier: rank %d / world %d out of range", rank, world);
+    }
+    KArgs k{};
+    k.rank       = rank;
+    k.world      = world;
+    k.flags      = flags;
+    k.timeout_ns = static_cast<uint64_t>(timeout_ms ? timeout_ms : kDefaultTimeoutMs) * 1000000ull;
+    for (int p = 0; p < world; ++p) {
+        if (!peer_ctrl[p]) {
+            return fu::fail(FU_E_ARG, "fu_barrier: no control block for rank %d", p);
+        }
+        k.peer_ctrl[p] = peer_ctrl[p];
+    }
+    k.own = peer_ctrl[rank];
+    barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream_v)>>>(k.own, k);
+    FU_CUDA_OK(cudaGetLastError());
+    return FU_OK;
+}

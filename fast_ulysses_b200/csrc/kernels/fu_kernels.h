@@ -1,0 +1,88 @@
+#pragma once
+// C interface of the sm_100a kernel library. Everything here takes raw device pointers and a CUDA
+// stream: the kernels never learn where a peer address came from (symmetric memory, IPC, or a fake
+// peer on the same device in a single-GPU test), and nothing in this library includes torch.
+//
+// Every launcher returns 0 on success or a negative FU_E_* code; fu_last_error() gives the text.
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FU_API __attribute__((visibility("default")))
+#define FU_MAX_WORLD 8
+
+enum {
+    FU_OK            = 0,
+    FU_E_ARG         = -1,  // an argument the launcher refuses before launching anything
+    FU_E_CUDA        = -2,  // a CUDA runtime/driver call failed
+    FU_E_UNSUPPORTED = -3,
+};
+
+// ---- control block ------------------------------------------------------------------------------
+// One per window, inside the same symmetric allocation, so that two collectives on two windows can
+// never disturb each other's handshake. `flags[p]` is written by rank p (remotely); everything else
+// is local to the owning rank.
+typedef struct FuCtrl {
+    uint64_t flags[FU_MAX_WORLD];  // last phase number rank p has announced to this rank
+    uint64_t epoch;                // phases this rank has completed on this window (+2 per call)
+    uint32_t arrive[2];            // CTA arrival counters used inside one launch
+    uint32_t status[6];            // [0] code, [1] peer, [2,3] expected, [4,5] seen (FU_ST_*)
+    uint64_t stamps[8];            // globaltimer ns: start, opened, pushed, closed, done
+    uint64_t pad_[11];
+} FuCtrl;  // 256 bytes
+
+#define FU_CTRL_BYTES 256
+
+enum {
+    FU_ST_OK            = 0,
+    FU_ST_OPEN_TIMEOUT  = 1,  // a peer never announced that it had finished reading the window
+    FU_ST_CLOSE_TIMEOUT = 2,  // a peer never announced that its writes had landed
+    FU_ST_COPY_TIMEOUT  = 3,  // a bulk copy inside the kernel did not complete
+};
+
+// ---- all-to-all -----------------------------------------------------------------------------------
+typedef struct FuRoute {
+    int32_t peer;
+    int32_t pad_;
+    int64_t src_off, dst_off;
+    int64_t src_pitch, dst_pitch;
+    int64_t row_bytes, rows;
+    int64_t batches, src_batch, dst_batch;
+} FuRoute;
+
+enum {
+    FU_A2A_NO_HANDSHAKE  = 1,   // skip both handshakes: single-device emulation of several ranks
+    FU_A2A_STAMPS        = 2,   // record per-phase globaltimer stamps into ctrl->stamps
+    FU_A2A_EARLY_PUBLISH = 4,   // TEST ONLY negative control: announce completion before the payload
+    FU_A2A_LDST          = 8,   // move data with 16-byte ld/st instead of bulk (TMA) copies
+    FU_A2A_MUTE          = 16,  // TEST ONLY: never announce anything, so that peers' waits run out
+};
+
+typedef struct FuA2AArgs {
+    const void* src;                    // this rank's input
+    void*       peer_win[FU_MAX_WORLD]; // window base on every rank (own entry included)
+    FuCtrl*     peer_ctrl[FU_MAX_WORLD];
+    void*       out;                    // if non-null: after the closing handshake copy the dense
+    int64_t     out_bytes;              //   prefix of the own window here (fused copy-out)
+    int32_t     rank, world;
+    int32_t     n_routes;
+    int32_t     flags;
+    int32_t     ctas;                   // 0 = library default
+    uint32_t    timeout_ms;             // bound on every cross-rank wait; 0 = library default
+    FuRoute     routes[FU_MAX_WORLD];
+} FuA2AArgs;
+
+FU_API int fu_a2a4d(const FuA2AArgs* args, void* stream);
+
+// Standalone cross-rank barrier on a window's control block (epoch += 1).
+FU_API int fu_barrier(FuCtrl* const* peer_ctrl, int rank, int world, uint32_t timeout_ms, int flags, void* stream);
+
+FU_API const char* fu_last_error(void);
+FU_API const char* fu_build_info(void);  // "sm_100a;<nvcc version>;<library version>"
+
+#ifdef __cplusplus
+}
+#endif

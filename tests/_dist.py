@@ -1,0 +1,53 @@
+"""Helpers to run a function on several CPU ranks (gloo) as child processes."""
+
+import os
+import socket
+import sys
+import traceback
+
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+
+def free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _entry(rank, world, port, fn_module, fn_name, args, errq):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    try:
+        import datetime
+
+        dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=60))
+        mod = __import__(fn_module)
+        getattr(mod, fn_name)(rank, world, *args)
+        dist.barrier()
+        dist.destroy_process_group()
+    except Exception:
+        errq.put((rank, traceback.format_exc()))
+        raise
+
+
+def run_ranks(world, fn_module, fn_name, *args, timeout=180):
+    ctx = mp.get_context("spawn")
+    errq = ctx.SimpleQueue()
+    port = free_port()
+    procs = [ctx.Process(target=_entry, args=(r, world, port, fn_module, fn_name, args, errq)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout)
+    hung = [p for p in procs if p.is_alive()]
+    for p in hung:
+        p.kill()  # exactly the processes started here
+    errors = []
+    while not errq.empty():
+        errors.append(errq.get())
+    assert not hung, f"{len(hung)} rank(s) did not finish within {timeout}s"
+    assert not errors, "\n".join(f"rank {r}:\n{tb}" for r, tb in errors)
+    assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
