@@ -1,0 +1,255 @@
+"""Headline benchmark: ms per Wan-720p bf16 ``all_to_all_4d`` (and, where built, the
+sequence-parallel attention block), device-timed, max over ranks.
+
+    python bench.py --gpus N --steps K --warmup W            # this library
+    python bench.py --impl reference --gpus N ...            # the unmodified reference build
+
+For N > 1 launch with ``python -m torch.distributed.run --nnodes=1 --nproc-per-node N ...``.
+Rank 0 prints exactly one JSON line.
+
+Config (the one the baseline names): 81 frames -> 21x45x80 = 75600 tokens in total, split evenly
+over the N ranks, 40 heads, d = 128, bf16, b = 1, mode 0 (scatter heads, gather sequence) through
+the public copying call. Total work is fixed as N grows (strong scaling). Timing: CUDA events
+around every step, L2 flushed between steps by writing a 256 MiB buffer, a barrier and a device
+synchronise on both sides of the timed region, the maximum over ranks reported.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+TOTAL_TOKENS, HEADS, HEAD_DIM = 75600, 40, 128
+PUBLISHED_MS = {8: 0.550, 4: 0.808}  # packed d=384 shape, reference README.md:37, docs/benchmark.md:202
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100", "-i",
+                 str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()  # the exact process started above
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for r in self.rows:
+            if len(r) < 7:
+                continue
+            try:
+                sm.append(float(r[0]))
+                mx.append(float(r[1]))
+            except ValueError:
+                continue
+            for name, v in zip(names, r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def setup_dist(n: int):
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    torch.cuda.set_device(local)
+    if world > 1 or n > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29511")
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", local))
+    return rank, local, world
+
+
+def max_over_ranks(v: float, world: int) -> float:
+    if world == 1:
+        return v
+    t = torch.tensor([v], device="cuda", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def sync_all(world: int):
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+def time_steps(step, steps: int, warmup: int, world: int, flush: torch.Tensor) -> float:
+    """ms per step, device-timed per step with an L2 flush in between, max over ranks."""
+    for _ in range(warmup):
+        flush.zero_()
+        step()
+    sync_all(world)
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+    ends = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+    for i in range(steps):
+        flush.zero_()
+        starts[i].record()
+        step()
+        ends[i].record()
+    sync_all(world)
+    total = sum(s.elapsed_time(e) for s, e in zip(starts, ends))
+    return max_over_ranks(total / steps, world)
+
+
+def make_group(impl: str, local: int, world: int):
+    if impl == "reference":
+        sys.path.insert(0, os.path.join(ROOT, "baseline", "_ref"))
+        import fast_ulysses  # the unmodified reference build
+
+        if not dist.is_initialized():
+            os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+            os.environ.setdefault("MASTER_PORT", "29512")
+            dist.init_process_group("nccl", rank=0, world_size=1, device_id=torch.device("cuda", local))
+        return fast_ulysses.UlyssesGroup(device=torch.device("cuda", local), require_nvlink=False)
+    import fast_ulysses_b200 as fu
+
+    return fu.UlyssesGroup(device=torch.device("cuda", local), require_nvlink=False)
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    ap.add_argument("--no-extras", action="store_true", help="skip the secondary measurements")
+    args = ap.parse_args()
+    warmup = max(3, args.warmup)
+
+    if args.impl == "reference" and not os.path.isdir(os.path.join(ROOT, "baseline", "_ref", "fast_ulysses")):
+        print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref holds no installed reference build"}))
+        return 0
+
+    rank, local, world = setup_dist(args.gpus)
+    try:
+        group = make_group(args.impl, local, world)
+    except Exception as e:  # the reference arm must report, not crash
+        if args.impl == "reference":
+            if rank == 0:
+                print(json.dumps({"impl": "reference", "unavailable": f"{type(e).__name__}: {str(e)[:200]}"}))
+            return 0
+        raise
+
+    dev = torch.device("cuda", local)
+    assert TOTAL_TOKENS % world == 0 and HEADS % world == 0, "bench.py runs even splits (N in 1, 2, 4, 8)"
+    s_local = TOTAL_TOKENS // world
+    torch.manual_seed(1234 + rank)
+    x = torch.randn(1, s_local, HEADS, HEAD_DIM, device=dev, dtype=torch.bfloat16)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def step():
+        return group.all_to_all_4d(x, mode=0)
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    ms = time_steps(step, args.steps, warmup, world, flush)
+    clocks = sampler.stop() if rank == 0 else {}
+
+    # end to end: the step's input arrives from pinned host memory, its result is read back
+    x_host = x.cpu().pin_memory()
+    probe_host = torch.empty(1024, dtype=torch.bfloat16).pin_memory()
+    x_dev = torch.empty_like(x)
+
+    def e2e_step():
+        x_dev.copy_(x_host, non_blocking=True)
+        y = group.all_to_all_4d(x_dev, mode=0)
+        probe_host.copy_(y.view(-1)[:1024], non_blocking=True)
+
+    e2e_ms = time_steps(e2e_step, max(3, args.steps // 5), warmup, world, flush)
+
+    extra = {}
+    if not args.no_extras:
+        y = step()
+        extra["mode1_ms"] = time_steps(lambda: group.all_to_all_4d(y, mode=1), args.steps, warmup, world, flush)
+        out = group.empty_output(x, mode=0)
+        extra["mode0_zero_copy_ms"] = time_steps(lambda: group.all_to_all_4d(x, mode=0, out=out), args.steps, warmup,
+                                                 world, flush)
+        del out, y
+        if world in PUBLISHED_MS:
+            # the shape the reference publishes: q, k, v packed (d = 384) with a 227-token text tail
+            s_pack = (75827 + world - 1) // world
+            xp = torch.randn(1, s_pack, HEADS, 3 * HEAD_DIM, device=dev, dtype=torch.bfloat16)
+            t = time_steps(lambda: group.all_to_all_4d(xp, mode=0), args.steps, warmup, world, flush)
+            extra["packed_d384"] = {"shape": [1, s_pack, HEADS, 3 * HEAD_DIM], "ms": t,
+                                    "published_reference_ms": PUBLISHED_MS[world],
+                                    "vs_published": t / PUBLISHED_MS[world]}
+            del xp
+        if args.impl == "ours":
+            try:
+                from fast_ulysses_b200.models.bench_block import bench_attention_block
+
+                extra["sp_attention_block"] = bench_attention_block(group, world, rank, time_steps, flush)
+            except ImportError:
+                pass
+    if hasattr(group, "check"):
+        group.check()
+
+    if rank == 0:
+        line = {
+            "metric": "ms per Wan-720p bf16 all_to_all_4d (mode 0, copying call), max over ranks",
+            "value": ms, "unit": "ms", "n_gpus": world, "steps": args.steps, "warmup": warmup, "ms_per_step": ms,
+            "higher_is_better": False, "scaling": "strong",
+            "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic (randn, seeded per rank)",
+            "config": {"model": "Wan2.1-14B 720p attention exchange", "global_batch": 1, "seq_len": TOTAL_TOKENS,
+                       "heads": HEADS, "head_dim": HEAD_DIM, "per_rank_shape": [1, s_local, HEADS, HEAD_DIM],
+                       "parallelism": f"sp{world}", "l2": "flushed between steps (256 MiB write)",
+                       "bytes_per_rank": x.numel() * 2},
+            "clocks": clocks,
+            "e2e": {"value": e2e_ms, "unit": "ms", "h2d_bytes_per_step": x.numel() * 2, "d2h_bytes_per_step": 2048},
+            "gpu_launches": args.steps if args.impl == "ours" else None,
+            "extra": extra,
+        }
+        if args.impl == "reference":
+            line["impl"] = "reference"
+            line.pop("gpu_launches")
+        if "packed_d384" in extra:
+            line["vs_baseline"] = extra["packed_d384"]["vs_published"]
+            line["vs_baseline_note"] = ("the published number is for the packed d=384 shape; vs_baseline compares "
+                                        "extra.packed_d384.ms with it, not the d=128 value")
+        print(json.dumps(line))
+    group.destroy()
+    if dist.is_initialized():
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

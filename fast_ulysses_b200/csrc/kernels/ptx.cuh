@@ -116,16 +116,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity)
         : "memory");
     return ok != 0;
 }
-// Bounded wait: returns false when `limit` polls pass without the phase completing. Every caller
-// must treat false as "give up, record an error, unwind" so that no kernel can spin for ever.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t limit = 20000000u)
+// Bounded wait: returns false when the phase has not completed within `limit_ns`. Every caller must
+// treat false as "give up, record an error, unwind" so that no kernel can spin for ever.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint64_t limit_ns = 2000000000ull)
 {
-    for (uint32_t i = 0; i < limit; ++i) {
+    if (mbar_try_wait(bar, parity)) {
+        return true;
+    }
+    const uint64_t t0 = globaltimer_ns();
+    for (uint32_t i = 1;; ++i) {
         if (mbar_try_wait(bar, parity)) {
             return true;
         }
+        if ((i & 255u) == 0u && (globaltimer_ns() - t0 > limit_ns || i > 0x7fffff00u)) {
+            return false;
+        }
     }
-    return false;
 }
 
 // ---- untiled bulk copies ------------------------------------------------------------------------

@@ -16,14 +16,19 @@ def free_port() -> int:
         return s.getsockname()[1]
 
 
-def _entry(rank, world, port, fn_module, fn_name, args, errq):
+def _entry(rank, world, port, fn_module, fn_name, args, errq, backend="gloo"):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
     sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
     sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
     try:
         import datetime
 
-        dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=60))
+        if backend == "nccl":
+            torch.cuda.set_device(rank)
+            dist.init_process_group("nccl", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=120),
+                                    device_id=torch.device("cuda", rank))
+        else:
+            dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=60))
         mod = __import__(fn_module)
         getattr(mod, fn_name)(rank, world, *args)
         dist.barrier()
@@ -33,11 +38,12 @@ def _entry(rank, world, port, fn_module, fn_name, args, errq):
         raise
 
 
-def run_ranks(world, fn_module, fn_name, *args, timeout=180):
+def run_ranks(world, fn_module, fn_name, *args, timeout=180, backend="gloo"):
     ctx = mp.get_context("spawn")
     errq = ctx.SimpleQueue()
     port = free_port()
-    procs = [ctx.Process(target=_entry, args=(r, world, port, fn_module, fn_name, args, errq)) for r in range(world)]
+    procs = [ctx.Process(target=_entry, args=(r, world, port, fn_module, fn_name, args, errq, backend))
+             for r in range(world)]
     for p in procs:
         p.start()
     for p in procs:

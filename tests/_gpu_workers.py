@@ -1,0 +1,354 @@
+"""Rank bodies for the multi-GPU tests: one process per GPU over NCCL. Every device-side wait in
+the library is bounded, so a protocol error ends as a status (checked with group.check()) or a
+mismatch, never as a hang. No test here faults, traps or hangs a GPU on purpose."""
+
+import torch
+import torch.distributed as dist
+
+from fast_ulysses_b200 import UlyssesGroup
+
+
+def ref_even(x, mode, world):
+    b, s, n, d = x.shape
+    if mode == 0:
+        t = x.reshape(b, s, world, n // world, d).permute(2, 0, 1, 3, 4).contiguous()
+        o = torch.empty_like(t)
+        dist.all_to_all_single(o, t)
+        return o.permute(1, 0, 2, 3, 4).reshape(b, world * s, n // world, d)
+    t = x.reshape(b, world, s // world, n, d).permute(1, 0, 2, 3, 4).contiguous()
+    o = torch.empty_like(t)
+    dist.all_to_all_single(o, t)
+    return o.permute(1, 2, 0, 3, 4).reshape(b, s // world, world * n, d)
+
+
+def ref_uneven(x, mode, seq, heads, rank, world):
+    b, d = x.shape[0], x.shape[3]
+    if mode == 0:
+        h0 = [sum(heads[:p]) for p in range(world)]
+        send = [x[:, :, h0[p]:h0[p] + heads[p]].contiguous() for p in range(world)]
+        recv = [torch.empty(b, seq[p], heads[rank], d, dtype=x.dtype, device=x.device) for p in range(world)]
+        dist.all_to_all(recv, send)
+        return torch.cat(recv, dim=1)
+    s0 = [sum(seq[:p]) for p in range(world)]
+    send = [x[:, s0[p]:s0[p] + seq[p]].contiguous() for p in range(world)]
+    recv = [torch.empty(b, seq[rank], heads[p], d, dtype=x.dtype, device=x.device) for p in range(world)]
+    dist.all_to_all(recv, send)
+    return torch.cat(recv, dim=2)
+
+
+def bits(t):
+    return t.contiguous().view(torch.uint8)
+
+
+def correctness(rank, world):
+    dev = torch.device("cuda", rank)
+    g = UlyssesGroup(device=dev)
+    fails = []
+
+    def expect(cond, what):
+        if not cond:
+            fails.append(what)
+
+    for flags, tag in ((0, "bulk"), (8, "ldst")):
+        g._handle.set_test_flags(flags)
+        for dtype in (torch.float16, torch.bfloat16):
+            for d in (64, 128, 384):
+                for mode in (0, 1):
+                    torch.manual_seed(100 + rank)
+                    shape = (2, 96, 2 * world, d) if mode == 0 else (2, 96 * world, 2, d)
+                    x = torch.randn(shape, device=dev, dtype=dtype)
+                    y = g.all_to_all_4d(x, mode=mode)
+                    expect(torch.equal(y, ref_even(x, mode, world)), f"{tag} even {dtype} d={d} mode={mode}")
+        # uneven: near-even and skewed
+        for seq, heads in (([97 + p for p in range(world)], [2 + (p % 2) for p in range(world)]),
+                           ([5 + 40 * p for p in range(world)], [1 + p for p in range(world)])):
+            torch.manual_seed(rank)
+            x0 = torch.randn(1, seq[rank], sum(heads), 128, device=dev, dtype=torch.bfloat16)
+            y0 = g.all_to_all_4d(x0, mode=0, seq_splits=seq, head_splits=heads)
+            expect(torch.equal(y0, ref_uneven(x0, 0, seq, heads, rank, world)), f"{tag} uneven mode 0 {seq}")
+            x1 = torch.randn(1, sum(seq), heads[rank], 128, device=dev, dtype=torch.bfloat16)
+            y1 = g.all_to_all_4d(x1, mode=1, seq_splits=seq, head_splits=heads)
+            expect(torch.equal(y1, ref_uneven(x1, 1, seq, heads, rank, world)), f"{tag} uneven mode 1 {seq}")
+            back = g.all_to_all_4d(y0, mode=1, seq_splits=seq, head_splits=heads)
+            expect(torch.equal(back, x0), f"{tag} round trip {seq}")
+    g._handle.set_test_flags(0)
+
+    # byte dtypes round trip
+    for dtype, d in ((torch.float32, 32), (torch.float8_e4m3fn, 64), (torch.float8_e5m2, 64), (torch.int8, 64),
+                     (torch.uint8, 64)):
+        x = torch.randint(0, 120, (1, 64, 2 * world, d), device=dev).to(dtype)
+        y = g.all_to_all_4d(x)
+        expect(torch.equal(bits(y), bits(ref_even(bits(x).reshape(1, 64, 2 * world, -1), 0, world))), f"bytes {dtype}")
+        expect(torch.equal(bits(g.all_to_all_4d(y, mode=1)), bits(x)), f"round trip {dtype}")
+
+    # out= plain, out=empty_output (zero-copy: internal window untouched), result survives next call
+    x = torch.randn(2, 128, 4 * world, 128, device=dev, dtype=torch.bfloat16)
+    want = ref_even(x, 0, world)
+    plain = torch.empty_like(want)
+    expect(g.all_to_all_4d(x, out=plain) is plain and torch.equal(plain, want), "out= plain")
+    e_sync = g._handle.epoch_debug(x, 0)
+    zc = g.empty_output(x)
+    g.all_to_all_4d(x, out=zc)
+    expect(torch.equal(zc, want), "out=empty_output")
+    expect(g._handle.epoch_debug(zc, 2) == 2 and g._handle.epoch_debug(x, 0) == e_sync, "zero-copy path taken")
+    kept = g.all_to_all_4d(x)
+    g.all_to_all_4d(torch.zeros_like(x))
+    expect(torch.equal(kept, want), "result survives the next call")
+
+    # 20 rounds on one window: +2 phases per call
+    e0 = g._handle.epoch_debug(x, 0)
+    for _ in range(20):
+        g.all_to_all_4d(x)
+    expect(g._handle.epoch_debug(x, 0) == e0 + 40, "epoch +2 per call")
+
+    # async: plain, non-contiguous input, out=, lend rotation, off the default stream
+    h = g.all_to_all_4d_async(x)
+    expect(torch.equal(h.wait(), want), "async")
+    xt = torch.randn(2, 4 * world, 128, 128, device=dev, dtype=torch.bfloat16).transpose(1, 2)
+    expect(torch.equal(g.all_to_all_4d_async(xt).wait(), ref_even(xt.contiguous(), 0, world)), "async strided")
+    o2 = torch.empty_like(want)
+    g.all_to_all_4d_async(x, out=o2).wait()
+    expect(torch.equal(o2, want), "async out=")
+    lent = [g.all_to_all_4d_async(x, lend=True) for _ in range(4)]
+    lent = [t.wait() for t in lent]
+    expect(len({t.data_ptr() for t in lent}) == 4 and all(torch.equal(t, want) for t in lent), "lend rotation")
+    del lent
+    side = torch.cuda.Stream(device=dev)
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        r = g.all_to_all_4d_async(x).wait()
+        expect(torch.equal(r, want), "async off the default stream")
+    torch.cuda.current_stream().wait_stream(side)
+    # five async calls in flight at once
+    many = [g.all_to_all_4d_async(x * (i + 1)) for i in range(5)]
+    for i, t in enumerate(many):
+        expect(torch.equal(t.wait(), ref_even(x * (i + 1), 0, world)), f"async in flight {i}")
+
+    # autograd: backward is the other mode with the same (unswapped) splits; double backward
+    seq, heads = [33 + 3 * p for p in range(world)], [1 + (p % 3) for p in range(world)]
+    xg = torch.randn(1, seq[rank], sum(heads), 64, device=dev, requires_grad=True)
+    yg = g.all_to_all_4d(xg, seq_splits=seq, head_splits=heads)
+    w = torch.randn_like(yg)
+    (yg * w).sum().backward()
+    expect(torch.equal(xg.grad, g.all_to_all_4d(w, mode=1, seq_splits=seq, head_splits=heads)), "backward")
+    import torch.autograd.forward_ad as fwAD
+
+    p_, t_ = torch.randn_like(xg), torch.randn_like(xg)
+    with fwAD.dual_level():
+        o = g.all_to_all_4d(fwAD.make_dual(p_, t_), seq_splits=seq, head_splits=heads)
+        _, tan = fwAD.unpack_dual(o)
+    expect(torch.equal(tan, g.all_to_all_4d(t_, seq_splits=seq, head_splits=heads)), "forward-mode tangent")
+
+    # the kernel's own phase timing moves the same bytes
+    yt, stages = g._timed(x)
+    expect(torch.equal(yt, want) and stages["transfer"] > 0 and len(stages) == 4, "timed")
+
+    # device barrier, then status
+    g.barrier()
+    g.check()
+    failed = torch.tensor([len(fails)], device=dev)
+    dist.all_reduce(failed)
+    g.destroy()
+    assert not fails, fails
+    assert failed.item() == 0
+
+
+def validation_uniform(rank, world):
+    """Rejections raise on every rank before the first handshake: the barrier after each case
+    would otherwise wait for a rank that went ahead."""
+    import pytest
+
+    dev = torch.device("cuda", rank)
+    g = UlyssesGroup(device=dev)
+    ok = torch.randn(1, 8, 2 * world, 64, device=dev, dtype=torch.bfloat16)
+
+    def rejects(fragment, fn, exc=RuntimeError):
+        with pytest.raises(exc, match=fragment):
+            fn()
+        dist.barrier()
+
+    rejects("must be a CUDA tensor", lambda: g.all_to_all_4d(ok.cpu()))
+    rejects("must be 4D", lambda: g.all_to_all_4d(ok[0]))
+    rejects("dtype must be", lambda: g.all_to_all_4d(ok.double()))
+    rejects("16-byte aligned", lambda: g.all_to_all_4d(ok[..., :4]))
+    rejects("mode must be 0 or 1", lambda: g.all_to_all_4d(ok, mode=3))
+    rejects("both seq_splits and head_splits", lambda: g.all_to_all_4d(ok, head_splits=[2] * world))
+    rejects("but the splits imply", lambda: g.all_to_all_4d(ok, seq_splits=[9] * world, head_splits=[2] * world))
+    rejects("must divide world_size",
+            lambda: g.all_to_all_4d(torch.randn(1, 8, 2 * world + 1, 64, device=dev, dtype=torch.bfloat16)))
+    rejects("moves no data", lambda: g.all_to_all_4d(ok[:, :0]))
+    rejects("out has shape", lambda: g.all_to_all_4d(ok, out=torch.empty(1, 8 * world, 3, 64, device=dev,
+                                                                         dtype=torch.bfloat16)))
+    rejects("out has dtype", lambda: g.all_to_all_4d(ok, out=torch.empty(1, 8 * world, 2, 64, device=dev)))
+    rejects("contiguous CUDA tensor", lambda: g.all_to_all_4d(
+        ok, out=torch.empty(1, 2, 8 * world, 64, device=dev, dtype=torch.bfloat16).transpose(1, 2)))
+    zc = g.empty_output(ok)
+    g.all_to_all_4d(ok, out=zc)
+    rejects("input overlaps the window", lambda: g.all_to_all_4d(_alias_of(zc, world), out=zc))
+    rejects("does not support autograd", lambda: g.all_to_all_4d(ok.clone().requires_grad_(), out=zc))
+    rejects("does not support autograd", lambda: g.all_to_all_4d_async(ok.clone().requires_grad_()))
+    rejects("not both", lambda: g.all_to_all_4d_async(ok, out=zc, lend=True), ValueError)
+    rejects("does not support torch.vmap", lambda: torch.vmap(lambda t: g.all_to_all_4d(t))(ok.unsqueeze(0)))
+    held = [g.all_to_all_4d_async(ok, lend=True).wait() for _ in range(4)]
+    rejects("lent results may be alive at once", lambda: g.all_to_all_4d_async(ok, lend=True))
+    del held
+    if torch.cuda.device_count() > world:
+        other = torch.device("cuda", world)
+        rejects("one group serves exactly one device", lambda: g.all_to_all_4d(ok.to(other)))
+    g.check()
+    g.destroy()
+    rejects("has been destroyed", lambda: g.all_to_all_4d(ok))
+    rejects("has been destroyed", lambda: g.all_to_all_4d_async(ok))
+
+
+def _alias_of(zc, world):
+    """An input of the right shape (1, 8, 2*world, 64) that lives inside the window behind `zc`."""
+    return zc.view(-1)[: 8 * 2 * world * 64].view(1, 8, 2 * world, 64)
+
+
+def ordering_control(rank, world):
+    """Payload visible when the flag arrives. ARMED (closing flag announced before the payload)
+    must tear on some rank; CLEAN must not. Uneven shards make rank 0's transfer the longest."""
+    dev = torch.device("cuda", rank)
+    g = UlyssesGroup(device=dev)
+    seq = [60000] + [2000] * (world - 1)
+    heads = [4] * world
+    x = torch.empty(1, seq[rank], sum(heads), 128, device=dev, dtype=torch.bfloat16)
+    out = g.empty_output(x, seq_splits=seq, head_splits=heads)
+
+    def torn_rounds(flags, rounds=24):
+        g._handle.set_test_flags(flags)
+        torn = 0
+        for i in range(rounds):
+            v = float(1 + (i % 100))
+            x.fill_(v)
+            g.all_to_all_4d(x, out=out, seq_splits=seq, head_splits=heads)
+            torn += int(not bool(torch.all(out == v)))
+        g._handle.set_test_flags(0)
+        t = torch.tensor([torn], device=dev)
+        dist.all_reduce(t)
+        return int(t.item())
+
+    clean = torn_rounds(0)
+    armed = torn_rounds(4)  # FU_A2A_EARLY_PUBLISH
+    g.check()
+    g.destroy()
+    assert clean == 0, f"CLEAN phase tore {clean} times"
+    if armed == 0:
+        print("BLIND: the armed control produced no stale read; the clean result proves less than it should")
+
+
+def graph_replay(rank, world):
+    dev = torch.device("cuda", rank)
+    g = UlyssesGroup(device=dev)
+    x = torch.randn(1, 2048, 4 * world, 128, device=dev, dtype=torch.bfloat16)
+    out = g.empty_output(x)
+    g.all_to_all_4d(x, out=out)
+    torch.cuda.synchronize()
+    dist.barrier()
+    e0 = g._handle.epoch_debug(out, 2)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        g.all_to_all_4d(x, out=out)
+    ballast = torch.randn(4096, 4096, device=dev)
+    for i in range(8):
+        x.copy_(torch.full_like(x, float(i + 1)))
+        if rank == i % world:
+            for _ in range(24):
+                ballast @ ballast  # skew one rank
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.all(out == float(i + 1)), f"replay {i} tore"
+    assert g._handle.epoch_debug(out, 2) == e0 + 16  # exactly two phases per replay
+    g.check()
+    g.destroy()
+
+
+def sync_async_coexist(rank, world):
+    """Sync and async calls on unordered streams use separate windows."""
+    dev = torch.device("cuda", rank)
+    g = UlyssesGroup(device=dev)
+    rounds = 200
+    xs = torch.empty(1, 256, 2 * world, 128, device=dev, dtype=torch.bfloat16)
+    bad = 0
+    for i in range(rounds):
+        a = torch.full_like(xs, float(i % 50))
+        b = torch.full_like(xs, float(100 + i % 50))
+        if rank == i % world:
+            torch.cuda._sleep(200000)
+        h = g.all_to_all_4d_async(a)
+        y1 = g.all_to_all_4d(b)
+        y2 = g.all_to_all_4d(b)
+        ya = h.wait()
+        bad += int(not (torch.all(ya == float(i % 50)) and torch.all(y1 == float(100 + i % 50))
+                        and torch.all(y2 == float(100 + i % 50))))
+    torch.cuda.synchronize()
+    assert g._handle.epoch_debug(xs, 0) == 4 * rounds and g._handle.epoch_debug(xs, 1) == 2 * rounds
+    g.check()
+    g.destroy()
+    assert bad == 0
+
+
+def window_reuse_race(rank, world):
+    """A peer's next call must not overwrite a window this rank is still reading: the opening
+    handshake makes writers wait for readers. One rotating slow reader per round."""
+    dev = torch.device("cuda", rank)
+    g = UlyssesGroup(device=dev)
+    x = torch.empty(1, 4096, 2 * world, 128, device=dev, dtype=torch.bfloat16)
+    out = g.empty_output(x)
+    bad = 0
+    for i in range(40):
+        x.fill_(float(i + 1))
+        g.all_to_all_4d(x, out=out)
+        if rank == i % world:
+            torch.cuda._sleep(2_000_000)  # a slow reader: its read of `out` is queued behind this
+        snapshot = out.clone()  # ordered on the caller's stream, before this rank's next call
+        bad += int(not bool(torch.all(snapshot == float(i + 1))))
+    g.check()
+    g.destroy()
+    assert bad == 0
+
+
+def subgroups_gpu(rank, world):
+    tp = 2
+    sp = world // tp
+    groups = [dist.new_group(list(range(t, world, tp))) for t in range(tp)]
+    mine = groups[rank % tp]
+    dev = torch.device("cuda", rank)
+    g = UlyssesGroup(mine, device=dev)
+    assert g.world_size == sp and g.rank == rank // tp
+    for it in range(10):
+        x = torch.randn(1, 64 + it, 2 * sp, 128, device=dev, dtype=torch.bfloat16)
+        y = g.all_to_all_4d(x)
+        b, s, n, d = x.shape
+        t = x.reshape(b, s, sp, n // sp, d).permute(2, 0, 1, 3, 4).contiguous()
+        o = torch.empty_like(t)
+        dist.all_to_all_single(o, t, group=mine)
+        assert torch.equal(y, o.permute(1, 0, 2, 3, 4).reshape(b, sp * s, n // sp, d))
+    g.check()
+    g.destroy()
+
+
+def peer_timeout_is_reported(rank, world):
+    """Host-made failure: one rank never announces (test flag), the others' bounded waits run out,
+    report through check(), and every context stays usable. Runs with plain peer loads/stores."""
+    dev = torch.device("cuda", rank)
+    g = UlyssesGroup(device=dev, timeout_ms=300)
+    x = torch.randn(1, 64, 2 * world, 64, device=dev, dtype=torch.bfloat16)
+    g.all_to_all_4d(x)  # window exists, clean round
+    g.check()
+    dist.barrier()
+    if rank == world - 1:
+        g._handle.set_test_flags(16)  # FU_A2A_MUTE
+    g.all_to_all_4d(x)
+    g._handle.set_test_flags(0)
+    raised = False
+    try:
+        g.check()
+    except RuntimeError as e:
+        raised = "timed out" in str(e) and f"waiting on rank {world - 1}" in str(e)
+    # the silent rank itself may or may not have run out of time waiting for the others
+    assert raised or rank == world - 1, "the missing announcement was not reported"
+    assert torch.ones(8, device=dev).sum().item() == 8  # context alive
+    dist.barrier()
+    g.destroy()
