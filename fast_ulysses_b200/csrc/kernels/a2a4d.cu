@@ -26,7 +26,9 @@ constexpr int      kStages      = 4;
 constexpr int      kStageBytes  = 48 * 1024;
 constexpr int      kAhead       = kStages - 2;  // loads issued this many chunks ahead of the stores
 constexpr int      kLdstThreads = 512;
-constexpr int      kDefaultCtas = 32;
+constexpr int      kLdstUnroll  = 8;           // 16-byte loads in flight per thread
+constexpr int      kLdstChunkBytes = 64 * 1024;  // = threads x unroll x 16 B: one pass per chunk
+constexpr int      kLdstCtasPerSm  = 2;
 constexpr uint32_t kDefaultTimeoutMs = 10000;
 
 // A route plus its decomposition into chunks of at most one stage.
@@ -242,12 +244,12 @@ __device__ void ldst_move(const RouteSet& set)
     while (cur.next(set, c)) {
         const uint32_t vpr  = c.row_bytes >> 4;
         const uint32_t nvec = vpr * c.nrows;
-        for (uint32_t v0 = threadIdx.x; v0 < nvec; v0 += 4 * blockDim.x) {
-            uint4    val[4];
-            uint8_t* dst[4];
+        for (uint32_t v0 = threadIdx.x; v0 < nvec; v0 += kLdstUnroll * kLdstThreads) {
+            uint4    val[kLdstUnroll];
+            uint8_t* dst[kLdstUnroll];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const uint32_t v = v0 + u * blockDim.x;
+            for (int u = 0; u < kLdstUnroll; ++u) {
+                const uint32_t v = v0 + u * kLdstThreads;
                 if (v < nvec) {
                     const uint32_t row = v / vpr;
                     const uint32_t col = v - row * vpr;
@@ -257,8 +259,8 @@ __device__ void ldst_move(const RouteSet& set)
                 }
             }
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                if (v0 + u * blockDim.x < nvec) {
+            for (int u = 0; u < kLdstUnroll; ++u) {
+                if (v0 + u * kLdstThreads < nvec) {
                     st_v4(dst[u], val[u]);
                 }
             }
@@ -268,14 +270,13 @@ __device__ void ldst_move(const RouteSet& set)
 
 // ---- the kernel ---------------------------------------------------------------------------------------
 template <bool kBulk>
-__global__ void __launch_bounds__(kBulk ? 32 : kLdstThreads, 1) a2a4d_kernel(const __grid_constant__ KArgs a)
+__global__ void __launch_bounds__(kBulk ? 32 : kLdstThreads, kBulk ? 1 : kLdstCtasPerSm) a2a4d_kernel(const __grid_constant__ KArgs a)
 {
     extern __shared__ __align__(1024) uint8_t smem[];
     __shared__ uint64_t                       full_bar[kStages];
     __shared__ uint32_t                       ticket_s;
 
     const int  warp      = threadIdx.x >> 5;
-    const int  lane      = threadIdx.x & 31;
     const bool handshake = !(a.flags & FU_A2A_NO_HANDSHAKE);
     const bool stamps    = (a.flags & FU_A2A_STAMPS) && blockIdx.x == 0 && threadIdx.x == 0;
     FuCtrl*    own       = a.own;
@@ -399,25 +400,31 @@ __global__ void __launch_bounds__(32, 1)
 }
 
 // ---- host side ----------------------------------------------------------------------------------------
-int decompose(RouteX& x)
+// Cuts a route into chunks of at most `chunk` bytes. A route that is dense on both sides is first
+// folded into one long row, so that its chunks are large whatever the row length was.
+void decompose(RouteX& x, int64_t chunk)
 {
     if (x.row_bytes <= 0 || x.rows <= 0 || x.batches <= 0) {
         x.count = 0;
-        return 0;
+        return;
     }
-    if (x.row_bytes <= kStageBytes) {
+    if (x.src_pitch == x.row_bytes && x.dst_pitch == x.row_bytes && x.rows > 1) {
+        x.row_bytes *= x.rows;
+        x.rows      = 1;
+        x.src_pitch = x.dst_pitch = x.row_bytes;
+    }
+    if (x.row_bytes <= chunk) {
         x.piece_bytes    = x.row_bytes;
         x.pieces_per_row = 1;
-        x.rows_per_chunk = static_cast<int32_t>(std::min<int64_t>(kStageBytes / x.row_bytes, x.rows));
+        x.rows_per_chunk = static_cast<int32_t>(std::min<int64_t>(chunk / x.row_bytes, x.rows));
     }
     else {
-        x.piece_bytes    = kStageBytes;
-        x.pieces_per_row = static_cast<int32_t>((x.row_bytes + kStageBytes - 1) / kStageBytes);
+        x.piece_bytes    = chunk;
+        x.pieces_per_row = static_cast<int32_t>((x.row_bytes + chunk - 1) / chunk);
         x.rows_per_chunk = 1;
     }
     x.row_groups = (x.rows + x.rows_per_chunk - 1) / x.rows_per_chunk;
     x.count      = x.batches * x.row_groups * x.pieces_per_row;
-    return 0;
 }
 
 bool aligned16(const void* p)
@@ -454,21 +461,22 @@ extern "C" int fu_a2a4d(const FuA2AArgs* args, void* stream_v)
     if (in.n_routes > 0 && !aligned16(in.src)) {
         return fu::fail(FU_E_ARG, "fu_a2a4d: the input is not 16-byte aligned");
     }
-    k.push.n = 0;
-    for (int i = 0; i < in.n_routes; ++i) {
-        const FuRoute& r = in.routes[i];
-        if (r.peer < 0 || r.peer >= in.world) {
-            return fu::fail(FU_E_ARG, "fu_a2a4d: route %d names rank %d", i, r.peer);
-        }
-        if ((r.row_bytes | r.src_off | r.dst_off | r.src_pitch | r.dst_pitch | r.src_batch | r.dst_batch) & 15) {
-            return fu::fail(FU_E_ARG, "fu_a2a4d: route %d is not 16-byte granular", i);
-        }
-        if (!aligned16(in.peer_win[r.peer])) {
-            return fu::fail(FU_E_ARG, "fu_a2a4d: rank %d's window is not 16-byte aligned", r.peer);
-        }
+    const bool    ldst  = (in.flags & FU_A2A_LDST) != 0;
+    const int64_t chunk = ldst ? kLdstChunkBytes : kStageBytes;
+    const bool    copy_out = in.out && in.out_bytes > 0;
+    if (copy_out && (!aligned16(in.out) || (in.out_bytes & 15))) {
+        return fu::fail(FU_E_ARG, "fu_a2a4d: the copy-out destination is not 16-byte granular");
+    }
+    if (in.n_out_routes < 0 || in.n_out_routes > 2) {
+        return fu::fail(FU_E_ARG, "fu_a2a4d: %d copy-out routes", in.n_out_routes);
+    }
+    auto granular = [](const FuRoute& r) {
+        return ((r.row_bytes | r.src_off | r.dst_off | r.src_pitch | r.dst_pitch | r.src_batch | r.dst_batch) & 15) == 0;
+    };
+    auto expand = [&](const FuRoute& r, const uint8_t* src_base, uint8_t* dst_base) {
         RouteX x{};
-        x.src       = static_cast<const uint8_t*>(in.src) + r.src_off;
-        x.dst       = static_cast<uint8_t*>(in.peer_win[r.peer]) + r.dst_off;
+        x.src       = src_base + r.src_off;
+        x.dst       = dst_base + r.dst_off;
         x.src_pitch = r.src_pitch;
         x.dst_pitch = r.dst_pitch;
         x.src_batch = r.src_batch;
@@ -476,54 +484,71 @@ extern "C" int fu_a2a4d(const FuA2AArgs* args, void* stream_v)
         x.rows      = r.rows;
         x.batches   = r.batches;
         x.row_bytes = r.row_bytes;
-        decompose(x);
+        decompose(x, chunk);
+        return x;
+    };
+    k.push.n = 0;
+    for (int i = 0; i < in.n_routes; ++i) {
+        const FuRoute& r = in.routes[i];
+        if (r.peer < 0 || r.peer >= in.world) {
+            return fu::fail(FU_E_ARG, "fu_a2a4d: route %d names rank %d", i, r.peer);
+        }
+        if (!granular(r)) {
+            return fu::fail(FU_E_ARG, "fu_a2a4d: route %d is not 16-byte granular", i);
+        }
+        if (!aligned16(in.peer_win[r.peer])) {
+            return fu::fail(FU_E_ARG, "fu_a2a4d: rank %d's window is not 16-byte aligned", r.peer);
+        }
+        // The own share never needs the window when the caller wants the result elsewhere.
+        const bool direct = copy_out && in.own_direct && r.peer == in.rank;
+        uint8_t*   dst    = direct ? static_cast<uint8_t*>(in.out) : static_cast<uint8_t*>(in.peer_win[r.peer]);
+        RouteX     x      = expand(r, static_cast<const uint8_t*>(in.src), dst);
         if (x.count > 0) {
             k.push.r[k.push.n++] = x;
             k.push.max_count     = std::max(k.push.max_count, x.count);
         }
     }
     k.copy_out.n = 0;
-    if (in.out && in.out_bytes > 0) {
-        if (!aligned16(in.out) || (in.out_bytes & 15)) {
-            return fu::fail(FU_E_ARG, "fu_a2a4d: the copy-out destination is not 16-byte granular");
+    if (copy_out) {
+        const uint8_t* win = static_cast<const uint8_t*>(in.peer_win[in.rank]);
+        if (in.n_out_routes > 0 || in.own_direct) {
+            for (int i = 0; i < in.n_out_routes; ++i) {
+                if (!granular(in.out_routes[i])) {
+                    return fu::fail(FU_E_ARG, "fu_a2a4d: copy-out route %d is not 16-byte granular", i);
+                }
+                RouteX x = expand(in.out_routes[i], win, static_cast<uint8_t*>(in.out));
+                if (x.count > 0) {
+                    k.copy_out.r[k.copy_out.n++] = x;
+                    k.copy_out.max_count         = std::max(k.copy_out.max_count, x.count);
+                }
+            }
         }
-        const int64_t whole = in.out_bytes / kStageBytes;
-        const int64_t tail  = in.out_bytes - whole * kStageBytes;
-        auto flat = [&](int64_t off, int64_t row_bytes, int64_t rows) {
-            RouteX x{};
-            x.src       = static_cast<const uint8_t*>(in.peer_win[in.rank]) + off;
-            x.dst       = static_cast<uint8_t*>(in.out) + off;
-            x.src_pitch = x.dst_pitch = row_bytes;
-            x.rows      = rows;
-            x.batches   = 1;
-            x.row_bytes = row_bytes;
-            decompose(x);
-            // one stage-sized chunk per row keeps every CTA's chunks far apart in memory
-            x.rows_per_chunk = 1;
-            x.row_groups     = rows;
-            x.count          = rows;
+        else {
+            FuRoute flat{};
+            flat.row_bytes = in.out_bytes;
+            flat.rows = flat.batches = 1;
+            flat.src_pitch = flat.dst_pitch = in.out_bytes;
+            RouteX x = expand(flat, win, static_cast<uint8_t*>(in.out));
             k.copy_out.r[k.copy_out.n++] = x;
-            k.copy_out.max_count         = std::max(k.copy_out.max_count, x.count);
-        };
-        if (whole > 0) {
-            flat(0, kStageBytes, whole);
-        }
-        if (tail > 0) {
-            flat(whole * kStageBytes, tail, 1);
+            k.copy_out.max_count         = x.count;
         }
     }
+    // `copy_out.n` doubles as "every CTA must see the closing handshake"; with nothing left to copy
+    // (a single rank whose own share went straight to `out`) the plain closing path is taken.
 
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
-    int          ctas   = in.ctas > 0 ? in.ctas : kDefaultCtas;
     int          dev = 0, sms = 0;
     FU_CUDA_OK(cudaGetDevice(&dev));
     FU_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-    // Every CTA must be resident at once: CTAs wait on one another's arrival counters.
-    ctas = std::max(1, std::min(ctas, sms));
+    // Every CTA must be resident at once (the CTAs that finish first wait for peers while the rest
+    // still have payload to push), so the grid never exceeds what the device can hold.
+    const int capacity = ldst ? sms * kLdstCtasPerSm : sms;
+    int       ctas     = in.ctas > 0 ? std::min(in.ctas, capacity) : capacity;
+    ctas               = std::max(1, ctas);
     if (k.push.n > 1 && ctas > k.push.n) {
         ctas -= ctas % k.push.n;  // a multiple of the route count pins each CTA to one peer
     }
-    if (in.flags & FU_A2A_LDST) {
+    if (ldst) {
         a2a4d_kernel<false><<<ctas, kLdstThreads, 0, stream>>>(k);
     }
     else {

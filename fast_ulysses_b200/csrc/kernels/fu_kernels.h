@@ -73,12 +73,64 @@ typedef struct FuA2AArgs {
     int32_t     ctas;                   // 0 = library default
     uint32_t    timeout_ms;             // bound on every cross-rank wait; 0 = library default
     FuRoute     routes[FU_MAX_WORLD];
+    // Copy-out refinement (append-only fields). When `own_direct` is set and `out` is given, the
+    // route whose peer is this rank writes straight into `out` instead of the window, and only
+    // the `n_out_routes` regions below (offsets relative to the window base and to `out` alike)
+    // are copied out after the closing handshake. With n_out_routes == 0 the whole dense prefix
+    // of `out_bytes` is copied.
+    int32_t     own_direct;
+    int32_t     n_out_routes;
+    FuRoute     out_routes[2];
 } FuA2AArgs;
 
 FU_API int fu_a2a4d(const FuA2AArgs* args, void* stream);
 
 // Standalone cross-rank barrier on a window's control block (epoch += 1).
 FU_API int fu_barrier(FuCtrl* const* peer_ctrl, int rank, int world, uint32_t timeout_ms, int flags, void* stream);
+
+// ---- tcgen05 GEMMs ------------------------------------------------------------------------------
+// C[m,n] = act(A[m,k] * B[n,k]^T + bias[n]) + residual[m,n]; bf16 operands, fp32 accumulation.
+// act: 0 none, 1 GELU (tanh form), 2 GELU (erf form). `err` (nullable) is a device word that
+// receives a non-zero code if a wait inside the kernel ran out.
+typedef struct FuGemmArgs {
+    const void*  a;
+    const void*  b;
+    void*        c;
+    int64_t      m, n, k, lda, ldb, ldc;
+    const float* bias;
+    const void*  residual;
+    int32_t      act;
+    int32_t      ctas;
+    uint32_t*    err;
+} FuGemmArgs;
+FU_API int fu_gemm_bf16(const FuGemmArgs* args, void* stream);
+
+// Fused mode-0 path: [q|k|v] = x * W^T (W rows ordered q heads, k heads, v heads; head_dim 128),
+// per-head RMSNorm and RoPE on q and k, each head-row stored into the owning rank's window at
+// (batch, seq_off + s, local head). Windows have layout (b, s_total, head_splits[p], 128) bf16.
+typedef struct FuQkvArgs {
+    const void*  x;
+    const void*  w;
+    int64_t      m, k, ldx, ldw;
+    int32_t      heads;
+    int32_t      pad_;
+    int64_t      s_local, seq_off, s_total;
+    const float* rope;     // (s_local, 64, 2): cos, sin per rotated pair
+    const float* gamma_q;  // (128)
+    const float* gamma_k;
+    float        eps;
+    int32_t      rank, world;
+    int32_t      head_splits[FU_MAX_WORLD];
+    void*        win_q[FU_MAX_WORLD];
+    void*        win_k[FU_MAX_WORLD];
+    void*        win_v[FU_MAX_WORLD];
+    FuCtrl*      peer_ctrl[FU_MAX_WORLD];
+    int32_t      flags;    // FU_A2A_NO_HANDSHAKE, FU_A2A_MUTE
+    uint32_t     timeout_ms;
+    int32_t      ctas;
+    uint32_t*    err;
+} FuQkvArgs;
+FU_API int fu_qkv_rope_scatter(const FuQkvArgs* args, void* stream);
 
 FU_API const char* fu_last_error(void);
 FU_API const char* fu_build_info(void);  // "sm_100a;<nvcc version>;<library version>"

@@ -1,0 +1,436 @@
+// tcgen05 GEMM kernels built on gemm_sm100.cuh:
+//
+//   fu_gemm_bf16          C = act(A * B^T + bias) + residual, bf16 in/out, fp32 accumulate.
+//   fu_qkv_rope_scatter   the fused mode-0 path: QKV projection whose epilogue applies per-head
+//                         RMSNorm and 3D RoPE to q and k in registers and stores every head-row
+//                         straight into the owning rank's q/k/v window at its permuted
+//                         (sequence-gathered, head-scattered) position over NVLink. The all-to-all
+//                         is the address of the store; there is no separate exchange or permute.
+//
+// The reference has no GEMM: its example wraps nn.Linear + separate norm/RoPE around two
+// all_to_all_4d calls (examples/dit_attention.py:45-63). These kernels replace that composition.
+#include "fu_kernels.h"
+#include "gemm_sm100.cuh"
+#include "host_util.h"
+#include "tma_host.h"
+
+#include <algorithm>
+
+namespace {
+
+using namespace fu;
+using namespace fu::gemm;
+
+// ---- plain epilogue --------------------------------------------------------------------------------
+struct PlainEpi {
+    __nv_bfloat16*       c;
+    const __nv_bfloat16* residual;
+    const float*         bias;
+    int64_t              ldc;
+    int                  M, N, act;
+
+    __device__ void open(int) {}
+    __device__ void close(int) {}
+
+    __device__ __forceinline__ static float gelu_tanh(float x)
+    {
+        const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+        return 0.5f * x * (1.0f + tanhf(u));
+    }
+    __device__ __forceinline__ static float gelu_erf(float x)
+    {
+        return 0.5f * x * (1.0f + erff(x * 0.7071067811865476f));
+    }
+
+    __device__ void tile(uint32_t tmem_acc, int mt, int nt, int quarter, int lane)
+    {
+        const int  row    = mt * BM + quarter * 32 + lane;
+        const bool row_ok = row < M;
+#pragma unroll 1
+        for (int chunk = 0; chunk < BN / 32; ++chunk) {
+            const int col0 = nt * BN + chunk * 32;
+            if (col0 >= N) {
+                break;  // warp-uniform
+            }
+            uint32_t r[32];
+            ptx::tmem_ld_32x32(tmem_acc + chunk * 32, r);
+            ptx::tmem_ld_wait();
+            if (!row_ok) {
+                continue;
+            }
+            float v[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                v[j] = __uint_as_float(r[j]);
+            }
+            if (bias) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    if (col0 + j < N) {
+                        v[j] += bias[col0 + j];
+                    }
+                }
+            }
+            if (act == 1) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    v[j] = gelu_tanh(v[j]);
+                }
+            }
+            else if (act == 2) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    v[j] = gelu_erf(v[j]);
+                }
+            }
+            __nv_bfloat16*       dst = c + static_cast<int64_t>(row) * ldc + col0;
+            const __nv_bfloat16* res = residual ? residual + static_cast<int64_t>(row) * ldc + col0 : nullptr;
+#pragma unroll
+            for (int g8 = 0; g8 < 4; ++g8) {
+                if (col0 + g8 * 8 + 8 <= N) {
+                    if (res) {
+                        const uint4 rv = *reinterpret_cast<const uint4*>(res + g8 * 8);
+                        const __nv_bfloat162* rp = reinterpret_cast<const __nv_bfloat162*>(&rv);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const float2 f = __bfloat1622float2(rp[j]);
+                            v[g8 * 8 + 2 * j] += f.x;
+                            v[g8 * 8 + 2 * j + 1] += f.y;
+                        }
+                    }
+                    uint4 o;
+                    o.x = pack_bf16(v[g8 * 8 + 0], v[g8 * 8 + 1]);
+                    o.y = pack_bf16(v[g8 * 8 + 2], v[g8 * 8 + 3]);
+                    o.z = pack_bf16(v[g8 * 8 + 4], v[g8 * 8 + 5]);
+                    o.w = pack_bf16(v[g8 * 8 + 6], v[g8 * 8 + 7]);
+                    *reinterpret_cast<uint4*>(dst + g8 * 8) = o;
+                }
+                else {
+                    for (int j = 0; j < 8; ++j) {
+                        if (col0 + g8 * 8 + j < N) {
+                            float x = v[g8 * 8 + j];
+                            if (res) {
+                                x += __bfloat162float(res[g8 * 8 + j]);
+                            }
+                            dst[g8 * 8 + j] = __float2bfloat16(x);
+                        }
+                    }
+                }
+            }
+        }
+    }
+};
+
+struct PlainArgs {
+    Core     core;
+    PlainEpi epi;
+};
+
+__global__ void __launch_bounds__(THREADS, 1) gemm_plain_kernel(const __grid_constant__ PlainArgs a)
+{
+    PlainEpi epi = a.epi;
+    run(a.core, epi);
+}
+
+// ---- fused QKV epilogue: RMSNorm + 3D RoPE + scatter ---------------------------------------------------
+constexpr int HEAD_DIM = 128;
+constexpr int MAX_HEADS = 128;
+
+struct QkvParams {
+    uint8_t*      win[3][FU_MAX_WORLD];  // q, k, v window base on every rank
+    Peers         peers;
+    const float2* rope;     // [s_local][64] (cos, sin) per rotated pair
+    const float*  gamma_q;  // [128]
+    const float*  gamma_k;
+    float         eps;
+    int           M, heads;          // rows = b * s_local; heads per projection
+    int64_t       s_local, seq_off, s_total;
+    uint8_t       owner[MAX_HEADS];  // head -> rank that owns it
+    uint8_t       local[MAX_HEADS];  // head -> index inside its owner's shard
+    uint8_t       heads_of[FU_MAX_WORLD];
+    int           handshake;
+};
+
+// The functor keeps a reference to the parameters (they stay in the kernel's constant bank) and
+// only its own mutable state in registers.
+struct QkvEpi {
+    const QkvParams& p;
+    uint64_t         base_epoch;
+
+    __device__ explicit QkvEpi(const QkvParams& params) : p(params), base_epoch(0) {}
+
+    __device__ void open(int epi_warp)
+    {
+        const Peers& peers     = p.peers;
+        const int    handshake = p.handshake;
+        base_epoch = *reinterpret_cast<volatile uint64_t*>(&peers.own->epoch);
+        if (handshake && epi_warp == 0) {
+            if (blockIdx.x == 0) {
+                hs_announce(peers, base_epoch + 1);
+            }
+            hs_await(peers, base_epoch + 1, FU_ST_OPEN_TIMEOUT);
+        }
+        epi_barrier();  // no epilogue thread stores to a peer before the owners said "go"
+    }
+
+    __device__ void close(int epi_tid)
+    {
+        __shared__ uint32_t ticket;
+        const Peers& peers     = p.peers;
+        const int    handshake = p.handshake;
+        ptx::fence_sys();
+        epi_barrier();
+        if (epi_tid == 0) {
+            ticket = atomicAdd(&peers.own->arrive[0], 1u);
+        }
+        epi_barrier();
+        if (ticket == gridDim.x - 1 && epi_tid < 32) {
+            if (handshake) {
+                ptx::fence_sys();
+                hs_announce(peers, base_epoch + 2);
+                hs_await(peers, base_epoch + 2, FU_ST_CLOSE_TIMEOUT);
+            }
+            if (epi_tid == 0) {
+                peers.own->arrive[0] = 0;
+                __threadfence();
+                *reinterpret_cast<volatile uint64_t*>(&peers.own->epoch) = base_epoch + 2;
+            }
+        }
+    }
+
+    __device__ void tile(uint32_t tmem_acc, int mt, int nt, int quarter, int lane)
+    {
+        const int     M = p.M, heads = p.heads;
+        const int64_t s_local = p.s_local, s_total = p.s_total, seq_off = p.seq_off;
+        const float   eps = p.eps;
+        const int     row    = mt * BM + quarter * 32 + lane;
+        const bool    row_ok = row < M;
+        const int64_t batch  = row / s_local;
+        const int64_t s      = row - batch * s_local;
+#pragma unroll 1
+        for (int hh = 0; hh < BN / HEAD_DIM; ++hh) {
+            const int head_global = nt * (BN / HEAD_DIM) + hh;
+            const int type        = head_global / heads;  // 0 q, 1 k, 2 v
+            if (type > 2) {
+                break;
+            }
+            const int      head  = head_global - type * heads;
+            const int      peer  = p.owner[head];
+            const int64_t  hp    = p.heads_of[peer];
+            uint8_t*       dst   = p.win[type][peer]
+                           + (((batch * s_total + seq_off + s) * hp + p.local[head]) * HEAD_DIM) * 2;
+            const uint32_t tcol  = tmem_acc + hh * HEAD_DIM;
+            float          scale = 1.0f;
+            if (type < 2) {
+                float ss = 0.0f;
+#pragma unroll 1
+                for (int chunk = 0; chunk < 4; ++chunk) {
+                    uint32_t r[32];
+                    ptx::tmem_ld_32x32(tcol + chunk * 32, r);
+                    ptx::tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const float x = __uint_as_float(r[j]);
+                        ss += x * x;
+                    }
+                }
+                scale = rsqrtf(ss * (1.0f / HEAD_DIM) + eps);
+            }
+            const float*  gamma = type == 0 ? p.gamma_q : p.gamma_k;
+            const float2* cs    = p.rope + (row_ok ? s : 0) * (HEAD_DIM / 2);
+#pragma unroll 1
+            for (int chunk = 0; chunk < 4; ++chunk) {
+                uint32_t r[32];
+                ptx::tmem_ld_32x32(tcol + chunk * 32, r);
+                ptx::tmem_ld_wait();
+                if (!row_ok) {
+                    continue;
+                }
+                uint32_t o[16];
+                if (type < 2) {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const int    c0 = chunk * 32 + 2 * i;
+                        const float  x0 = __uint_as_float(r[2 * i]) * scale * gamma[c0];
+                        const float  x1 = __uint_as_float(r[2 * i + 1]) * scale * gamma[c0 + 1];
+                        const float2 t  = cs[chunk * 16 + i];
+                        o[i]            = pack_bf16(x0 * t.x - x1 * t.y, x0 * t.y + x1 * t.x);
+                    }
+                }
+                else {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        o[i] = pack_bf16(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+                    }
+                }
+                uint4* out = reinterpret_cast<uint4*>(dst + chunk * 64);
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4) {
+                    ptx::st_v4(out + q4, make_uint4(o[4 * q4], o[4 * q4 + 1], o[4 * q4 + 2], o[4 * q4 + 3]));
+                }
+            }
+        }
+    }
+};
+
+struct QkvArgs {
+    Core      core;
+    QkvParams epi;
+};
+
+__global__ void __launch_bounds__(THREADS, 1) qkv_rope_scatter_kernel(const __grid_constant__ QkvArgs a)
+{
+    QkvEpi epi(a.epi);
+    run(a.core, epi);
+}
+
+int launch_grid(int ctas, int tiles)
+{
+    int dev = 0, sms = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    int g = ctas > 0 ? std::min(ctas, sms) : sms;
+    return std::max(1, std::min(g, tiles));
+}
+
+template <class K>
+int set_smem(K kernel)
+{
+    static bool done[64] = {};
+    int         dev      = 0;
+    FU_CUDA_OK(cudaGetDevice(&dev));
+    if (dev < 64 && !done[dev]) {
+        FU_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        done[dev] = true;
+    }
+    return FU_OK;
+}
+
+int fill_core(Core& core, const void* a, const void* b, int64_t m, int64_t n, int64_t k, int64_t lda, int64_t ldb,
+              uint32_t* err)
+{
+    if (m <= 0 || n <= 0 || k <= 0) {
+        return fu::fail(FU_E_ARG, "gemm: empty problem (m=%lld n=%lld k=%lld)", (long long)m, (long long)n, (long long)k);
+    }
+    if (k % 8) {
+        return fu::fail(FU_E_ARG, "gemm: k=%lld must be a multiple of 8 (16-byte rows for TMA)", (long long)k);
+    }
+    int rc = make_map_2d(&core.map_a, a, 2, m, k, lda, BM, BK);
+    if (rc != FU_OK) {
+        return rc;
+    }
+    rc = make_map_2d(&core.map_b, b, 2, n, k, ldb, BN, BK);
+    if (rc != FU_OK) {
+        return rc;
+    }
+    core.M       = static_cast<int>(m);
+    core.N       = static_cast<int>(n);
+    core.K       = static_cast<int>(k);
+    core.tiles_m = static_cast<int>((m + BM - 1) / BM);
+    core.tiles_n = static_cast<int>((n + BN - 1) / BN);
+    core.err     = err;
+    return FU_OK;
+}
+
+}  // namespace
+
+extern "C" int fu_gemm_bf16(const FuGemmArgs* g, void* stream)
+{
+    if (!g || !g->a || !g->b || !g->c) {
+        return fu::fail(FU_E_ARG, "fu_gemm_bf16: null operand");
+    }
+    if ((g->ldc % 8) || (reinterpret_cast<uintptr_t>(g->c) & 15u)
+        || (g->residual && (reinterpret_cast<uintptr_t>(g->residual) & 15u))) {
+        return fu::fail(FU_E_ARG, "fu_gemm_bf16: C (and the residual) need 16-byte aligned rows");
+    }
+    PlainArgs a{};
+    int       rc = fill_core(a.core, g->a, g->b, g->m, g->n, g->k, g->lda, g->ldb, g->err);
+    if (rc != FU_OK) {
+        return rc;
+    }
+    a.epi.c        = static_cast<__nv_bfloat16*>(g->c);
+    a.epi.residual = static_cast<const __nv_bfloat16*>(g->residual);
+    a.epi.bias     = g->bias;
+    a.epi.ldc      = g->ldc;
+    a.epi.M        = a.core.M;
+    a.epi.N        = a.core.N;
+    a.epi.act      = g->act;
+    rc             = set_smem(gemm_plain_kernel);
+    if (rc != FU_OK) {
+        return rc;
+    }
+    const int grid = launch_grid(g->ctas, a.core.tiles_m * a.core.tiles_n);
+    gemm_plain_kernel<<<grid, THREADS, SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(a);
+    FU_CUDA_OK(cudaGetLastError());
+    return FU_OK;
+}
+
+extern "C" int fu_qkv_rope_scatter(const FuQkvArgs* q, void* stream)
+{
+    if (!q || !q->x || !q->w || !q->rope || !q->gamma_q || !q->gamma_k) {
+        return fu::fail(FU_E_ARG, "fu_qkv_rope_scatter: null operand");
+    }
+    if (q->world < 1 || q->world > FU_MAX_WORLD || q->rank < 0 || q->rank >= q->world) {
+        return fu::fail(FU_E_ARG, "fu_qkv_rope_scatter: rank %d / world %d", q->rank, q->world);
+    }
+    if (q->heads < 1 || q->heads > MAX_HEADS || (3 * q->heads) % 2) {
+        return fu::fail(FU_E_ARG, "fu_qkv_rope_scatter: heads=%d (need an even 3*heads <= %d)", q->heads, 3 * MAX_HEADS);
+    }
+    if (q->s_local <= 0 || q->m % q->s_local) {
+        return fu::fail(FU_E_ARG, "fu_qkv_rope_scatter: m=%lld is not a multiple of s_local=%lld", (long long)q->m,
+                        (long long)q->s_local);
+    }
+    QkvArgs a{};
+    int     rc = fill_core(a.core, q->x, q->w, q->m, 3LL * q->heads * HEAD_DIM, q->k, q->ldx, q->ldw, q->err);
+    if (rc != FU_OK) {
+        return rc;
+    }
+    QkvParams& e = a.epi;
+    int     h = 0;
+    for (int p = 0; p < q->world; ++p) {
+        if (q->head_splits[p] < 0 || q->head_splits[p] > 255) {
+            return fu::fail(FU_E_ARG, "fu_qkv_rope_scatter: head_splits[%d]=%d", p, q->head_splits[p]);
+        }
+        e.heads_of[p] = static_cast<uint8_t>(q->head_splits[p]);
+        for (int i = 0; i < q->head_splits[p]; ++i, ++h) {
+            if (h >= MAX_HEADS) {
+                return fu::fail(FU_E_ARG, "fu_qkv_rope_scatter: too many heads");
+            }
+            e.owner[h] = static_cast<uint8_t>(p);
+            e.local[h] = static_cast<uint8_t>(i);
+        }
+        if (!q->win_q[p] || !q->win_k[p] || !q->win_v[p] || !q->peer_ctrl[p]) {
+            return fu::fail(FU_E_ARG, "fu_qkv_rope_scatter: no window for rank %d", p);
+        }
+        e.win[0][p]     = static_cast<uint8_t*>(q->win_q[p]);
+        e.win[1][p]     = static_cast<uint8_t*>(q->win_k[p]);
+        e.win[2][p]     = static_cast<uint8_t*>(q->win_v[p]);
+        e.peers.ctrl[p] = q->peer_ctrl[p];
+    }
+    if (h != q->heads) {
+        return fu::fail(FU_E_ARG, "fu_qkv_rope_scatter: head_splits sum to %d, expected %d", h, q->heads);
+    }
+    e.peers.own        = q->peer_ctrl[q->rank];
+    e.peers.rank       = q->rank;
+    e.peers.world      = q->world;
+    e.peers.mute       = (q->flags & FU_A2A_MUTE) ? 1 : 0;
+    e.peers.timeout_ns = static_cast<uint64_t>(q->timeout_ms ? q->timeout_ms : 10000) * 1000000ull;
+    e.handshake        = (q->flags & FU_A2A_NO_HANDSHAKE) ? 0 : 1;
+    e.rope             = reinterpret_cast<const float2*>(q->rope);
+    e.gamma_q          = q->gamma_q;
+    e.gamma_k          = q->gamma_k;
+    e.eps              = q->eps;
+    e.M                = a.core.M;
+    e.heads            = q->heads;
+    e.s_local          = q->s_local;
+    e.seq_off          = q->seq_off;
+    e.s_total          = q->s_total;
+    rc                 = set_smem(qkv_rope_scatter_kernel);
+    if (rc != FU_OK) {
+        return rc;
+    }
+    const int grid = launch_grid(q->ctas, a.core.tiles_m * a.core.tiles_n);
+    qkv_rope_scatter_kernel<<<grid, THREADS, SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(a);
+    FU_CUDA_OK(cudaGetLastError());
+    return FU_OK;
+}

@@ -437,7 +437,7 @@ at::Tensor all_to_all_4d_autograd(const GroupPtr& group, const at::Tensor& input
 
 // ---- plan debug ----------------------------------------------------------------------------------------------
 // The plan as tensors, so that a CPU test can replay it over plain byte arrays for any rank.
-std::tuple<std::vector<int64_t>, int64_t, at::Tensor, at::Tensor> a2a_plan_debug(
+std::tuple<std::vector<int64_t>, int64_t, at::Tensor, at::Tensor, at::Tensor> a2a_plan_debug(
     int64_t b, int64_t d, int64_t rank, int64_t world, std::vector<int64_t> seq, std::vector<int64_t> heads,
     int64_t mode, int64_t elem_size)
 {
@@ -468,7 +468,7 @@ std::tuple<std::vector<int64_t>, int64_t, at::Tensor, at::Tensor> a2a_plan_debug
         }
         return t;
     };
-    return {plan.out_shape, plan.window_numel, pack(plan.sends), pack(plan.recvs)};
+    return {plan.out_shape, plan.window_numel, pack(plan.sends), pack(plan.recvs), pack(plan.from_peers)};
 }
 
 }  // namespace fu
@@ -543,7 +543,7 @@ TORCH_LIBRARY(fast_ulysses_b200, m)
     refuse_batching("all_to_all_4d_timed");
 
     m.def("a2a_plan_debug(int b, int d, int rank, int world_size, int[] seq_splits, int[] head_splits, "
-          "int mode, int elem_size) -> (int[], int, Tensor, Tensor)",
+          "int mode, int elem_size) -> (int[], int, Tensor, Tensor, Tensor)",
           &fu::a2a_plan_debug);
 }
 

@@ -191,6 +191,33 @@ Plan make_plan(const Geometry& g, int mode, int64_t elem_size, const std::vector
             plan.recvs.push_back(in);
         }
     }
+    // Complement of the own share inside the output.
+    const std::vector<int64_t> s0 = starts_of(g.seq);
+    const std::vector<int64_t> h0 = starts_of(g.heads);
+    auto region = [&](int64_t off, int64_t row_bytes, int64_t rows, int64_t pitch, int64_t batch) {
+        if (row_bytes <= 0 || rows <= 0) {
+            return;
+        }
+        Route r;
+        r.peer      = g.rank;
+        r.src_off   = r.dst_off = off;
+        r.src_pitch = r.dst_pitch = pitch;
+        r.row_bytes = row_bytes;
+        r.rows      = rows;
+        r.batches   = g.b;
+        r.src_batch = r.dst_batch = batch;
+        plan.from_peers.push_back(r);
+    };
+    if (mode == kScatterHeads) {
+        const int64_t w = n_me * d_bytes;  // rows of the output are w bytes, back to back
+        region(0, w, s0[g.rank], w, S * w);
+        region((s0[g.rank] + s_me) * w, w, S - s0[g.rank] - s_me, w, S * w);
+    }
+    else {
+        const int64_t pitch = N * d_bytes;
+        region(0, h0[g.rank] * d_bytes, s_me, pitch, s_me * pitch);
+        region((h0[g.rank] + n_me) * d_bytes, (N - h0[g.rank] - n_me) * d_bytes, s_me, pitch, s_me * pitch);
+    }
     return plan;
 }
 

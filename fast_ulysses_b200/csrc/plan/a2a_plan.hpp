@@ -58,6 +58,10 @@ struct Plan {
     int64_t              out_numel    = 0;
     std::vector<Route>   sends;
     std::vector<Route>   recvs;
+    // The parts of this rank's output that PEERS write (everything but the own share), as at most
+    // two regions with src_off == dst_off relative to the window and to a caller-owned output
+    // alike. A copying call sends the own share straight to the output and copies out only these.
+    std::vector<Route>   from_peers;
 };
 
 // `in_strides` (elements, for dims b, s, n; the last dim must be dense and the head stride must be

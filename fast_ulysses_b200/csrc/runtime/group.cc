@@ -335,6 +335,24 @@ void Group::launch(const Plan& plan, const void* src, const Window& w, void* out
         }
     }
     a.n_routes = n;
+    if (out) {
+        // Own share straight into the caller's tensor; only what peers wrote is copied out.
+        a.own_direct   = 1;
+        a.n_out_routes = 0;
+        for (const Route& r : plan.from_peers) {
+            FuRoute& o  = a.out_routes[a.n_out_routes++];
+            o.peer      = rank_;
+            o.src_off   = r.src_off;
+            o.dst_off   = r.dst_off;
+            o.src_pitch = r.src_pitch;
+            o.dst_pitch = r.dst_pitch;
+            o.row_bytes = r.row_bytes;
+            o.rows      = r.rows;
+            o.batches   = r.batches;
+            o.src_batch = r.src_batch;
+            o.dst_batch = r.dst_batch;
+        }
+    }
     const int rc = fu_a2a4d(&a, stream);
     TORCH_CHECK(rc == FU_OK, "fast_ulysses_b200: ", fu_last_error());
 }

@@ -30,7 +30,8 @@ class FuA2AArgs(C.Structure):
     _fields_ = [("src", C.c_void_p), ("peer_win", C.c_void_p * FU_MAX_WORLD),
                 ("peer_ctrl", C.c_void_p * FU_MAX_WORLD), ("out", C.c_void_p), ("out_bytes", C.c_int64),
                 ("rank", C.c_int32), ("world", C.c_int32), ("n_routes", C.c_int32), ("flags", C.c_int32),
-                ("ctas", C.c_int32), ("timeout_ms", C.c_uint32), ("routes", FuRoute * FU_MAX_WORLD)]
+                ("ctas", C.c_int32), ("timeout_ms", C.c_uint32), ("routes", FuRoute * FU_MAX_WORLD),
+                ("own_direct", C.c_int32), ("n_out_routes", C.c_int32), ("out_routes", FuRoute * 2)]
 
 
 _lib = None
@@ -50,6 +51,9 @@ def lib() -> C.CDLL:
         _lib.fu_build_info.restype = C.c_char_p
         _lib.fu_a2a4d.argtypes = [C.POINTER(FuA2AArgs), C.c_void_p]
         _lib.fu_a2a4d.restype = C.c_int
+        for name in ("fu_gemm_bf16", "fu_qkv_rope_scatter"):
+            getattr(_lib, name).restype = C.c_int
+            getattr(_lib, name).argtypes = [C.c_void_p, C.c_void_p]
     return _lib
 
 
@@ -62,3 +66,26 @@ def route_from_row(row) -> FuRoute:
     """A row of ``a2a_plan_debug``'s route tensor -> FuRoute."""
     peer, src_off, dst_off, src_pitch, dst_pitch, row_bytes, rows, batches, src_batch, dst_batch = (int(v) for v in row)
     return FuRoute(peer, 0, src_off, dst_off, src_pitch, dst_pitch, row_bytes, rows, batches, src_batch, dst_batch)
+
+
+class FuGemmArgs(C.Structure):
+    _fields_ = [("a", C.c_void_p), ("b", C.c_void_p), ("c", C.c_void_p), ("m", C.c_int64), ("n", C.c_int64),
+                ("k", C.c_int64), ("lda", C.c_int64), ("ldb", C.c_int64), ("ldc", C.c_int64), ("bias", C.c_void_p),
+                ("residual", C.c_void_p), ("act", C.c_int32), ("ctas", C.c_int32), ("err", C.c_void_p)]
+
+
+class FuQkvArgs(C.Structure):
+    _fields_ = [("x", C.c_void_p), ("w", C.c_void_p), ("m", C.c_int64), ("k", C.c_int64), ("ldx", C.c_int64),
+                ("ldw", C.c_int64), ("heads", C.c_int32), ("pad_", C.c_int32), ("s_local", C.c_int64),
+                ("seq_off", C.c_int64), ("s_total", C.c_int64), ("rope", C.c_void_p), ("gamma_q", C.c_void_p),
+                ("gamma_k", C.c_void_p), ("eps", C.c_float), ("rank", C.c_int32), ("world", C.c_int32),
+                ("head_splits", C.c_int32 * FU_MAX_WORLD), ("win_q", C.c_void_p * FU_MAX_WORLD),
+                ("win_k", C.c_void_p * FU_MAX_WORLD), ("win_v", C.c_void_p * FU_MAX_WORLD),
+                ("peer_ctrl", C.c_void_p * FU_MAX_WORLD), ("flags", C.c_int32), ("timeout_ms", C.c_uint32),
+                ("ctas", C.c_int32), ("err", C.c_void_p)]
+
+
+def stream_ptr():
+    import torch
+
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)

@@ -1,0 +1,98 @@
+"""bf16 GEMM on the tcgen05 tensor cores (csrc/kernels/gemm_sm100.cu).
+
+``gemm_bf16(a, b)`` computes ``a @ b.T`` with fp32 accumulation in tensor memory; bias, GELU and a
+residual add are fused into the epilogue. Both operands must have a contiguous last (K) axis.
+``linear`` wraps it as a differentiable ``F.linear``: the backward runs two more of these GEMMs on
+transposed copies, so every contraction of the block stays on this kernel.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import _ckernels as ck
+
+_err_words: dict[int, torch.Tensor] = {}
+
+
+def error_word(device: torch.device) -> torch.Tensor:
+    """One device word per GPU that kernels set when one of their bounded waits ran out."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    if idx not in _err_words:
+        _err_words[idx] = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
+    return _err_words[idx]
+
+
+def check_errors(device: torch.device | None = None) -> None:
+    """Synchronising: raises if any tcgen05 kernel on this device gave up on a wait."""
+    device = device or torch.device("cuda", torch.cuda.current_device())
+    code = int(error_word(device).item())
+    if code:
+        error_word(device).zero_()
+        raise RuntimeError(f"fast_ulysses_b200: a tcgen05 kernel gave up on an internal wait (code {code})")
+
+
+def gemm_bf16(a: torch.Tensor, b: torch.Tensor, *, bias: torch.Tensor | None = None,
+              residual: torch.Tensor | None = None, act: int = 0, out: torch.Tensor | None = None,
+              ctas: int = 0) -> torch.Tensor:
+    """``out[m, n] = act(a[m, :] . b[n, :] + bias[n]) + residual[m, n]`` (bf16 in, bf16 out)."""
+    assert a.is_cuda and b.is_cuda and a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
+    assert a.dim() == 2 and b.dim() == 2 and a.shape[1] == b.shape[1], (a.shape, b.shape)
+    if a.stride(1) != 1:
+        a = a.contiguous()
+    if b.stride(1) != 1:
+        b = b.contiguous()
+    m, k = a.shape
+    n = b.shape[0]
+    if out is None:
+        out = torch.empty(m, n, dtype=torch.bfloat16, device=a.device)
+    assert out.shape == (m, n) and out.stride(1) == 1 and out.dtype == torch.bfloat16
+    g = ck.FuGemmArgs()
+    g.a, g.b, g.c = a.data_ptr(), b.data_ptr(), out.data_ptr()
+    g.m, g.n, g.k = m, n, k
+    g.lda, g.ldb, g.ldc = a.stride(0), b.stride(0), out.stride(0)
+    if bias is not None:
+        assert bias.dtype == torch.float32 and bias.numel() == n and bias.is_contiguous()
+        g.bias = bias.data_ptr()
+    if residual is not None:
+        assert residual.dtype == torch.bfloat16 and residual.shape == (m, n) and residual.stride(0) == out.stride(0)
+        g.residual = residual.data_ptr()
+    g.act = act
+    g.ctas = ctas
+    g.err = error_word(a.device).data_ptr()
+    lib = ck.lib()
+    ck.check(lib.fu_gemm_bf16(C.byref(g), ck.stream_ptr()))
+    return out
+
+
+class _Linear(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, bias):
+        x2 = x.reshape(-1, x.shape[-1])
+        ctx.save_for_backward(x2, weight)
+        ctx.has_bias = bias is not None
+        ctx.x_shape = x.shape
+        y = gemm_bf16(x2, weight, bias=bias.float() if bias is not None else None)
+        return y.view(*x.shape[:-1], weight.shape[0])
+
+    @staticmethod
+    def backward(ctx, gy):
+        x2, weight = ctx.saved_tensors
+        gy2 = gy.reshape(-1, gy.shape[-1]).contiguous()
+        gx = gw = gb = None
+        if ctx.needs_input_grad[0]:
+            # dX[m, k] = sum_n dY[m, n] W[n, k]  ->  A = dY (m x n), B = W^T (k x n)
+            gx = gemm_bf16(gy2, weight.t().contiguous()).view(ctx.x_shape)
+        if ctx.needs_input_grad[1]:
+            # dW[n, k] = sum_m dY[m, n] X[m, k]  ->  A = dY^T (n x m), B = X^T (k x m)
+            gw = gemm_bf16(gy2.t().contiguous(), x2.t().contiguous())
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            gb = gy2.float().sum(0).to(gy.dtype)
+        return gx, gw, gb
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
+    """Differentiable ``x @ weight.T + bias`` on the tcgen05 GEMM (bf16)."""
+    return _Linear.apply(x, weight, bias)

@@ -1,0 +1,67 @@
+"""The fused mode-0 path: QKV projection + per-head RMSNorm + 3D RoPE + head scatter in one kernel.
+
+``qkv_rope_scatter_raw`` launches csrc/kernels/gemm_sm100.cu:fu_qkv_rope_scatter on raw window
+pointers (this is what single-GPU tests use, with fake peers on one device). The differentiable,
+group-aware wrapper lives in :mod:`fast_ulysses_b200.models.attention`.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import _ckernels as ck
+from .gemm import error_word
+
+HEAD_DIM = 128
+
+
+def qkv_rope_scatter_raw(x: torch.Tensor, w: torch.Tensor, rope: torch.Tensor, gamma_q: torch.Tensor,
+                         gamma_k: torch.Tensor, *, heads: int, s_local: int, seq_off: int, s_total: int,
+                         head_splits: list[int], rank: int, win_q: list[int], win_k: list[int], win_v: list[int],
+                         ctrl: list[int], eps: float = 1e-6, flags: int = 0, timeout_ms: int = 10000,
+                         ctas: int = 0) -> None:
+    """x: (b * s_local, hidden) bf16, w: (3 * heads * 128, hidden) bf16 (rows: q heads, k heads,
+    v heads). Each rank's q/k/v window has layout (b, s_total, head_splits[p], 128) bf16."""
+    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.stride(1) == 1 and w.stride(1) == 1
+    assert w.shape[0] == 3 * heads * HEAD_DIM and w.shape[1] == x.shape[1]
+    assert rope.dtype == torch.float32 and rope.shape == (s_local, HEAD_DIM // 2, 2) and rope.is_contiguous()
+    world = len(head_splits)
+    a = ck.FuQkvArgs()
+    a.x, a.w = x.data_ptr(), w.data_ptr()
+    a.m, a.k, a.ldx, a.ldw = x.shape[0], x.shape[1], x.stride(0), w.stride(0)
+    a.heads = heads
+    a.s_local, a.seq_off, a.s_total = s_local, seq_off, s_total
+    a.rope, a.gamma_q, a.gamma_k = rope.data_ptr(), gamma_q.data_ptr(), gamma_k.data_ptr()
+    assert gamma_q.dtype == torch.float32 and gamma_k.dtype == torch.float32
+    a.eps = eps
+    a.rank, a.world = rank, world
+    for p in range(world):
+        a.head_splits[p] = head_splits[p]
+        a.win_q[p], a.win_k[p], a.win_v[p], a.peer_ctrl[p] = win_q[p], win_k[p], win_v[p], ctrl[p]
+    a.flags, a.timeout_ms, a.ctas = flags, timeout_ms, ctas
+    a.err = error_word(x.device).data_ptr()
+    ck.check(ck.lib().fu_qkv_rope_scatter(C.byref(a), ck.stream_ptr()))
+
+
+def qkv_reference(x: torch.Tensor, w: torch.Tensor, rope: torch.Tensor, gamma_q: torch.Tensor,
+                  gamma_k: torch.Tensor, heads: int, eps: float = 1e-6):
+    """fp32 PyTorch statement: matmul -> per-head RMSNorm (q, k) -> RoPE (q, k). Returns q, k, v
+    of shape (b*s, heads, 128) for the local rows (before any exchange)."""
+    from .rope import apply_rope_reference
+
+    y = x.float() @ w.float().t()
+    q, k, v = (t.reshape(x.shape[0], heads, HEAD_DIM) for t in y.chunk(3, dim=1))
+
+    def norm(t, g):
+        return t * torch.rsqrt(t.pow(2).mean(-1, keepdim=True) + eps) * g.float()
+
+    s_local = rope.shape[0]
+    b = x.shape[0] // s_local
+
+    def rot(t):
+        t = t.reshape(b, s_local, heads, HEAD_DIM)
+        return apply_rope_reference(t, rope).reshape(-1, heads, HEAD_DIM)
+
+    return rot(norm(q, gamma_q)), rot(norm(k, gamma_k)), v

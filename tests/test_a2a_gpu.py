@@ -33,7 +33,7 @@ def shards(glob, seq, heads, mode):
     return (by_seq, by_head) if mode == 0 else (by_head, by_seq)
 
 
-def emulate(b, seq, heads, d, mode, dtype, flags, copy_out, ctas=0):
+def emulate(b, seq, heads, d, mode, dtype, flags, copy_out, ctas=0, own_direct=True):
     ws = len(seq)
     glob = global_tensor(b, sum(seq), sum(heads), d, dtype)
     inputs, expected = shards(glob, seq, heads, mode)
@@ -63,11 +63,18 @@ def emulate(b, seq, heads, d, mode, dtype, flags, copy_out, ctas=0):
             if with_out:
                 a.out = outs[r].data_ptr()
                 a.out_bytes = outs[r].numel() * elem
+                if own_direct:
+                    a.own_direct = 1
+                    keep = plans[r][4].tolist()
+                    a.n_out_routes = len(keep)
+                    for i, row in enumerate(keep):
+                        a.out_routes[i] = ck.route_from_row(row)
             ck.check(ck.lib().fu_a2a4d(C.byref(a), C.c_void_p(stream)))
     torch.cuda.synchronize()
     for r in range(ws):
         n = expected[r].numel()
         got = wins[r][: n * elem].view(dtype).reshape(expected[r].shape)
+        # pass 1 (no output tensor) filled the whole window, the own share included
         assert torch.equal(got.view(torch.uint8), expected[r].view(torch.uint8)), f"window of rank {r}"
         if copy_out:
             assert torch.equal(outs[r].view(torch.uint8), expected[r].view(torch.uint8)), f"copy-out of rank {r}"
@@ -95,6 +102,12 @@ def test_uneven_and_empty_shards(flags, mode):
 def test_dtypes(dtype, d):
     for mode in (0, 1):
         emulate(2, [5, 9, 2], [3, 1, 2], d, mode, dtype, 0, copy_out=True)
+
+
+@pytest.mark.parametrize("flags", [0, ck.FU_A2A_LDST], ids=["bulk", "ldst"])
+def test_flat_copy_out_without_own_direct(flags):
+    emulate(2, [17, 5, 33], [2, 3, 1], 64, 0, torch.bfloat16, flags, copy_out=True, own_direct=False)
+    emulate(2, [17, 5, 33], [2, 3, 1], 64, 1, torch.bfloat16, flags, copy_out=True, own_direct=False)
 
 
 def test_rows_wider_than_a_stage_and_many_chunks():

@@ -1,0 +1,72 @@
+"""tcgen05 GEMM against a plain PyTorch fp32 statement of the same op."""
+
+import pytest
+import torch
+
+from fast_ulysses_b200.ops import gemm
+
+pytestmark = pytest.mark.gpu
+
+
+def rel_err(got, want):
+    return ((got.float() - want).norm() / want.norm().clamp_min(1e-12)).item()
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (128, 256, 256), (300, 512, 256), (1000, 384, 320),
+                                   (77, 40, 72), (2048, 1536, 1024)])
+def test_gemm_matches_fp32(m, n, k):
+    torch.manual_seed(m + n + k)
+    a = torch.randn(m, k, device="cuda").bfloat16()
+    b = torch.randn(n, k, device="cuda").bfloat16()
+    got = gemm.gemm_bf16(a, b)
+    gemm.check_errors()
+    want = a.float() @ b.float().t()
+    assert got.shape == (m, n)
+    assert rel_err(got, want) < 5e-3, rel_err(got, want)
+    assert torch.allclose(got.float(), want, atol=0.5, rtol=2e-2)
+
+
+@pytest.mark.parametrize("act", [0, 1, 2])
+def test_fused_epilogue(act):
+    torch.manual_seed(act)
+    m, n, k = 520, 776, 192
+    a = torch.randn(m, k, device="cuda").bfloat16()
+    b = (torch.randn(n, k, device="cuda") * 0.1).bfloat16()
+    bias = torch.randn(n, device="cuda")
+    res = torch.randn(m, n, device="cuda").bfloat16()
+    got = gemm.gemm_bf16(a, b, bias=bias, residual=res, act=act)
+    gemm.check_errors()
+    y = a.float() @ b.float().t() + bias
+    if act == 1:
+        y = torch.nn.functional.gelu(y, approximate="tanh")
+    elif act == 2:
+        y = torch.nn.functional.gelu(y)
+    want = y + res.float()
+    assert rel_err(got, want) < 6e-3, rel_err(got, want)
+
+
+def test_strided_operands_and_many_tiles_per_cta():
+    a_full = torch.randn(700, 1024, device="cuda").bfloat16()
+    a = a_full[:, 128:640]  # leading dimension larger than k
+    b = torch.randn(1024, 512, device="cuda").bfloat16()
+    got = gemm.gemm_bf16(a, b, ctas=3)  # 6 x 4 tiles over 3 CTAs: accumulator buffers and ring wrap
+    gemm.check_errors()
+    assert rel_err(got, a.float() @ b.float().t()) < 5e-3
+
+
+def test_linear_autograd():
+    torch.manual_seed(0)
+    x = torch.randn(3, 200, 256, device="cuda").bfloat16().requires_grad_()
+    w = (torch.randn(384, 256, device="cuda") * 0.05).bfloat16().requires_grad_()
+    bias = torch.randn(384, device="cuda").bfloat16().requires_grad_()
+    y = gemm.linear(x, w, bias)
+    gy = torch.randn_like(y)
+    y.backward(gy)
+    gemm.check_errors()
+    xr, wr, br = (t.detach().float().requires_grad_() for t in (x, w, bias))
+    yr = torch.nn.functional.linear(xr, wr, br)
+    yr.backward(gy.float())
+    assert rel_err(y, yr.detach()) < 5e-3
+    assert rel_err(x.grad, xr.grad) < 6e-3
+    assert rel_err(w.grad, wr.grad) < 6e-3
+    assert rel_err(bias.grad, br.grad) < 6e-3

@@ -136,6 +136,44 @@ def test_matches_torch_all_to_all_semantics():
         assert np.array_equal(got, w.numpy())
 
 
+@pytest.mark.parametrize("mode", [0, 1])
+@pytest.mark.parametrize("seq,heads", [([5, 7, 3], [3, 1, 2]), ([4, 0, 6], [2, 2, 0]), ([6], [3])])
+def test_own_share_direct_plus_from_peers_covers_the_output(mode, seq, heads):
+    """The copying call: own share straight to the output, `from_peers` regions copied out of the
+    window. Together they must produce exactly the full output, and must not overlap."""
+    b, d, dtype = 2, 4, np.float32
+    ws = len(seq)
+    inputs, expected = make_inputs(b, seq, heads, d, mode, dtype, seed=5)
+    outs_win, plans = replay(b, seq, heads, d, mode, inputs)
+    elem = 4
+    for r in range(ws):
+        want = expected[r]
+        out = np.full(want.size * elem, 0xAB, dtype=np.uint8)
+        written = np.zeros(want.size * elem, dtype=np.int32)
+        src = inputs[r].reshape(-1).view(np.uint8)
+        win = outs_win[r].reshape(-1).view(np.uint8)
+        for op in routes(plans[r][2]):
+            if op["peer"] != r:
+                continue
+            for bi in range(op["batches"]):
+                for row in range(op["rows"]):
+                    so = op["src_off"] + bi * op["src_batch"] + row * op["src_pitch"]
+                    do = op["dst_off"] + bi * op["dst_batch"] + row * op["dst_pitch"]
+                    out[do:do + op["row_bytes"]] = src[so:so + op["row_bytes"]]
+                    written[do:do + op["row_bytes"]] += 1
+        regions = routes(plans[r][4])
+        assert len(regions) <= 2
+        for op in regions:
+            assert op["src_off"] == op["dst_off"] and op["src_pitch"] == op["dst_pitch"]
+            for bi in range(op["batches"]):
+                for row in range(op["rows"]):
+                    o = op["src_off"] + bi * op["src_batch"] + row * op["src_pitch"]
+                    out[o:o + op["row_bytes"]] = win[o:o + op["row_bytes"]]
+                    written[o:o + op["row_bytes"]] += 1
+        assert np.all(written == 1), f"rank {r}: every output byte written exactly once"
+        assert np.array_equal(out, want.reshape(-1).view(np.uint8))
+
+
 def test_window_numel_is_max_over_ranks():
     seq, heads = [5, 7, 3], [3, 1, 2]
     for mode in (0, 1):
