@@ -541,10 +541,19 @@ extern "C" int fu_a2a4d(const FuA2AArgs* args, void* stream_v)
     FU_CUDA_OK(cudaGetDevice(&dev));
     FU_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
     // Every CTA must be resident at once (the CTAs that finish first wait for peers while the rest
-    // still have payload to push), so the grid never exceeds what the device can hold.
+    // still have payload to push), so the grid never exceeds what the device can hold. Two
+    // collectives of one rank may run side by side on unordered streams (the sync and the async
+    // call); if each could fill the device, rank A might hold every SM with the one while rank B
+    // holds every SM with the other, each waiting for the peer's other kernel to start. So with
+    // peers a launch takes two thirds of the device, or one third when flagged as the minor
+    // partner, and both always fit together. A single rank waits for nobody and takes it all.
     const int capacity = ldst ? sms * kLdstCtasPerSm : sms;
-    int       ctas     = in.ctas > 0 ? std::min(in.ctas, capacity) : capacity;
-    ctas               = std::max(1, ctas);
+    int       share    = capacity;
+    if (in.world > 1) {
+        share = (in.flags & FU_A2A_MINOR_SHARE) ? capacity / 3 : (2 * capacity) / 3;
+    }
+    int ctas = in.ctas > 0 ? std::min(in.ctas, share) : share;
+    ctas     = std::max(1, ctas);
     if (k.push.n > 1 && ctas > k.push.n) {
         ctas -= ctas % k.push.n;  // a multiple of the route count pins each CTA to one peer
     }

@@ -1,0 +1,453 @@
+// Non-causal flash attention forward for head_dim 128 on the tcgen05 tensor cores.
+//
+// One persistent CTA per SM works on (batch, head, 256 query rows) items: two 128-row query tiles
+// that share every K/V tile. Warp roles:
+//   warp 0       TMA producer: Q (once per item), then K and V tiles through two-stage rings
+//   warp 1       MMA issuer: S_t = Q_t K^T (operands in shared memory), O_t += P_t V (P read
+//                from tensor memory, V as an MN-major shared-memory operand)
+//   warps 2..5   softmax for query tile 0, warps 6..9 for query tile 1: one thread per row;
+//                exp2 with a lazily updated reference maximum, P written back over S in tensor
+//                memory as packed bf16, O rescaled in tensor memory only when the maximum grew by
+//                more than 2^8; final normalisation, bf16 store and log-sum-exp
+// Tensor memory (512 columns): S0 | S1 | O0 | O1, 128 fp32 columns each; P_t aliases S_t.
+// The two query tiles are staggered (QK of tile 0 for step j+1 is issued between the two PV of
+// step j), so each softmax has two MMA slots of cover.
+//
+// q, k, v, o use the (batch, seq, heads, 128) layout of the all-to-all windows, so attention reads
+// what the fused QKV kernel scattered and writes what the output projection pulls, with no copy.
+// The reference has no attention kernel (examples/dit_attention.py:57 calls torch SDPA).
+#include "fu_kernels.h"
+#include "host_util.h"
+#include "ptx.cuh"
+#include "tma_host.h"
+
+#include <cuda_bf16.h>
+
+#include <algorithm>
+
+namespace {
+
+using namespace fu;
+
+constexpr int D         = 128;
+constexpr int BM        = 128;  // rows per query tile
+constexpr int QT        = 2;    // query tiles per CTA
+constexpr int BN        = 128;  // kv rows per step
+constexpr int KV_STAGES = 2;
+constexpr int TILE_BYTES = 128 * D * 2;       // 32 KiB: a 128 x 128 bf16 tile as two 64-column halves
+constexpr int HALF_BYTES = TILE_BYTES / 2;
+constexpr int SMEM_BYTES = (QT + 2 * KV_STAGES) * TILE_BYTES + 1024;
+constexpr int THREADS    = 32 * 10;
+constexpr float RESCALE_THRESHOLD = 8.0f;     // in log2 units
+
+enum : uint32_t { ERR_LOAD = 11, ERR_MMA = 12, ERR_SOFTMAX = 13 };
+
+struct Params {
+    CUtensorMap    map_q, map_k, map_v;
+    __nv_bfloat16* o;
+    float*         lse;         // (B, H, Sq)
+    int64_t        o_row, o_head, o_batch;  // element strides of o
+    int            B, H, Sq, Skv;
+    int            q_blocks, total_work, n_kv;
+    float          scale, scale_log2;
+    uint32_t*      err;
+};
+
+__device__ __forceinline__ void flag(const Params& p, uint32_t code)
+{
+    if (p.err) {
+        atomicCAS(p.err, 0u, code);
+    }
+}
+
+struct Barriers {
+    uint64_t q_full, q_empty;
+    uint64_t k_full[KV_STAGES], k_empty[KV_STAGES], v_full[KV_STAGES], v_empty[KV_STAGES];
+    uint64_t s_full[QT], p_ready[QT], o_final[QT], o_free[QT];
+};
+
+__global__ void __launch_bounds__(THREADS, 1) fmha_fwd_kernel(const __grid_constant__ Params p)
+{
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ Barriers       bar;
+    __shared__ uint32_t       tmem_holder;
+
+    const uint32_t base = (ptx::smem_addr(smem_raw) + 1023u) & ~1023u;
+    uint8_t*       sm   = smem_raw + (base - ptx::smem_addr(smem_raw));
+    // layout: Q0 | Q1 | K[0] | K[1] | V[0] | V[1]
+    const uint32_t sq_addr = base;
+    const uint32_t sk_addr = base + QT * TILE_BYTES;
+    const uint32_t sv_addr = sk_addr + KV_STAGES * TILE_BYTES;
+    uint8_t*       sq      = sm;
+    uint8_t*       sk      = sm + QT * TILE_BYTES;
+    uint8_t*       sv      = sk + KV_STAGES * TILE_BYTES;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        ptx::mbar_init(&bar.q_full, 1);
+        ptx::mbar_init(&bar.q_empty, 1);
+        for (int s = 0; s < KV_STAGES; ++s) {
+            ptx::mbar_init(&bar.k_full[s], 1);
+            ptx::mbar_init(&bar.k_empty[s], 1);
+            ptx::mbar_init(&bar.v_full[s], 1);
+            ptx::mbar_init(&bar.v_empty[s], 1);
+        }
+        for (int t = 0; t < QT; ++t) {
+            ptx::mbar_init(&bar.s_full[t], 1);
+            ptx::mbar_init(&bar.p_ready[t], 128);
+            ptx::mbar_init(&bar.o_final[t], 1);
+            ptx::mbar_init(&bar.o_free[t], 128);
+        }
+        ptx::mbar_fence_init();
+        ptx::tma_prefetch_desc(&p.map_q);
+        ptx::tma_prefetch_desc(&p.map_k);
+        ptx::tma_prefetch_desc(&p.map_v);
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc<512>(&tmem_holder);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::tc_fence_after();
+    const uint32_t tmem = tmem_holder;
+    const int      n_kv = p.n_kv;
+
+    if (warp == 0) {
+        // ---------------------------------------------------------------- producer
+        if (lane == 0) {
+            uint32_t it = 0, wc = 0;
+            bool     ok = true;
+            for (int w = blockIdx.x; w < p.total_work && ok; w += gridDim.x, ++wc) {
+                const int qb = w % p.q_blocks;
+                const int h  = (w / p.q_blocks) % p.H;
+                const int b  = w / (p.q_blocks * p.H);
+                if (!ptx::mbar_wait(&bar.q_empty, (wc & 1u) ^ 1u)) {
+                    flag(p, ERR_LOAD);
+                    break;
+                }
+                ptx::mbar_expect_tx(&bar.q_full, QT * TILE_BYTES);
+                for (int t = 0; t < QT; ++t) {
+                    for (int half = 0; half < 2; ++half) {
+                        ptx::tma_load_4d(sq + t * TILE_BYTES + half * HALF_BYTES, &p.map_q, half * 64,
+                                         qb * (QT * BM) + t * BM, h, b, &bar.q_full);
+                    }
+                }
+                for (int j = 0; j < n_kv; ++j, ++it) {
+                    const int      s      = it % KV_STAGES;
+                    const uint32_t parity = ((it / KV_STAGES) & 1u) ^ 1u;
+                    if (!ptx::mbar_wait(&bar.k_empty[s], parity)) {
+                        flag(p, ERR_LOAD);
+                        ok = false;
+                        break;
+                    }
+                    ptx::mbar_expect_tx(&bar.k_full[s], TILE_BYTES);
+                    for (int half = 0; half < 2; ++half) {
+                        ptx::tma_load_4d(sk + s * TILE_BYTES + half * HALF_BYTES, &p.map_k, half * 64, j * BN, h, b,
+                                         &bar.k_full[s]);
+                    }
+                    if (!ptx::mbar_wait(&bar.v_empty[s], parity)) {
+                        flag(p, ERR_LOAD);
+                        ok = false;
+                        break;
+                    }
+                    ptx::mbar_expect_tx(&bar.v_full[s], TILE_BYTES);
+                    for (int half = 0; half < 2; ++half) {
+                        ptx::tma_load_4d(sv + s * TILE_BYTES + half * HALF_BYTES, &p.map_v, half * 64, j * BN, h, b,
+                                         &bar.v_full[s]);
+                    }
+                }
+            }
+        }
+        __syncwarp();
+    }
+    else if (warp == 1) {
+        // ---------------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc_qk = ptx::make_idesc(1, 1, BM, BN, 0, 0);  // both K-major
+            constexpr uint32_t idesc_pv = ptx::make_idesc(1, 1, BM, D, 0, 1);   // V is MN-major
+            uint32_t           it = 0, wc = 0;
+            uint32_t           pcount[QT] = {0, 0};
+            bool               ok = true;
+
+            auto issue_qk = [&](int t, int stage) {
+                const uint32_t qa = sq_addr + t * TILE_BYTES;
+                const uint32_t ka = sk_addr + stage * TILE_BYTES;
+#pragma unroll
+                for (int kk = 0; kk < D / 16; ++kk) {
+                    const uint32_t off = (kk >> 2) * HALF_BYTES + (kk & 3) * 32;
+                    ptx::mma_f16_ss(tmem + t * 128, ptx::smem_desc_sw128(qa + off, 16, 1024),
+                                    ptx::smem_desc_sw128(ka + off, 16, 1024), idesc_qk, kk != 0);
+                }
+                ptx::mma_commit(&bar.s_full[t]);
+            };
+            auto issue_pv = [&](int t, int stage, bool accumulate) {
+                const uint32_t va = sv_addr + stage * TILE_BYTES;
+#pragma unroll
+                for (int kk = 0; kk < BN / 16; ++kk) {
+                    // 16 kv rows = 2048 bytes further down; the two 64-wide halves of d are
+                    // HALF_BYTES apart (leading byte offset), 8-row groups 1024 bytes apart
+                    ptx::mma_f16_ts(tmem + 256 + t * 128, tmem + t * 128 + kk * 8,
+                                    ptx::smem_desc_sw128(va + kk * 2048, HALF_BYTES, 1024), idesc_pv,
+                                    accumulate || kk != 0);
+                }
+            };
+
+            for (int w = blockIdx.x; w < p.total_work && ok; w += gridDim.x, ++wc) {
+                if (!ptx::mbar_wait(&bar.q_full, wc & 1u)) {
+                    flag(p, ERR_MMA);
+                    break;
+                }
+                // prologue: S for both query tiles of kv step 0
+                {
+                    const int s = it % KV_STAGES;
+                    if (!ptx::mbar_wait(&bar.k_full[s], (it / KV_STAGES) & 1u)) {
+                        flag(p, ERR_MMA);
+                        break;
+                    }
+                    ptx::tc_fence_after();
+                    issue_qk(0, s);
+                    issue_qk(1, s);
+                    ptx::mma_commit(&bar.k_empty[s]);
+                }
+                for (int j = 0; j < n_kv && ok; ++j, ++it) {
+                    const int  s    = it % KV_STAGES;
+                    const int  sn   = (it + 1) % KV_STAGES;
+                    const bool more = j + 1 < n_kv;
+                    if (!ptx::mbar_wait(&bar.v_full[s], (it / KV_STAGES) & 1u)) {
+                        flag(p, ERR_MMA);
+                        ok = false;
+                        break;
+                    }
+                    if (more && !ptx::mbar_wait(&bar.k_full[sn], ((it + 1) / KV_STAGES) & 1u)) {
+                        flag(p, ERR_MMA);
+                        ok = false;
+                        break;
+                    }
+                    for (int t = 0; t < QT; ++t) {
+                        if (!ptx::mbar_wait(&bar.p_ready[t], pcount[t] & 1u)) {
+                            flag(p, ERR_MMA);
+                            ok = false;
+                            break;
+                        }
+                        ++pcount[t];
+                        if (j == 0 && !ptx::mbar_wait(&bar.o_free[t], (wc & 1u) ^ 1u)) {
+                            flag(p, ERR_MMA);
+                            ok = false;
+                            break;
+                        }
+                        ptx::tc_fence_after();
+                        issue_pv(t, s, j != 0);
+                        if (!more) {
+                            ptx::mma_commit(&bar.o_final[t]);
+                        }
+                        else {
+                            issue_qk(t, sn);  // S_t is free again: PV_t above is ordered before it
+                        }
+                    }
+                    if (!ok) {
+                        break;
+                    }
+                    ptx::mma_commit(&bar.v_empty[s]);
+                    if (more) {
+                        ptx::mma_commit(&bar.k_empty[sn]);
+                    }
+                }
+                ptx::mma_commit(&bar.q_empty);
+            }
+        }
+        __syncwarp();
+    }
+    else {
+        // ---------------------------------------------------------------- softmax + epilogue
+        const int      t       = (warp - 2) >> 2;          // query tile
+        const int      quarter = warp & 3;                 // TMEM lane quarter of this warp
+        const int      row_in  = quarter * 32 + lane;      // row inside the query tile
+        const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
+        const uint32_t ts      = tmem + t * 128 + lane_off;        // S_t / P_t
+        const uint32_t to      = tmem + 256 + t * 128 + lane_off;  // O_t
+        const float    c       = p.scale_log2;
+        uint32_t       scount = 0, wc = 0;
+        bool           ok = true;
+
+        for (int w = blockIdx.x; w < p.total_work && ok; w += gridDim.x, ++wc) {
+            const int qb  = w % p.q_blocks;
+            const int h   = (w / p.q_blocks) % p.H;
+            const int b   = w / (p.q_blocks * p.H);
+            const int row = qb * (QT * BM) + t * BM + row_in;
+            float     m_ref = -INFINITY, l = 0.0f;
+
+            for (int j = 0; j < n_kv; ++j, ++scount) {
+                if (!ptx::mbar_wait(&bar.s_full[t], scount & 1u)) {
+                    flag(p, ERR_SOFTMAX);
+                    ok = false;
+                    break;
+                }
+                ptx::tc_fence_after();
+                const int valid = min(BN, p.Skv - j * BN);  // columns of this step that exist
+                // pass 1: row maximum
+                float mx = -INFINITY;
+#pragma unroll 1
+                for (int ch = 0; ch < 4; ++ch) {
+                    uint32_t r[32];
+                    ptx::tmem_ld_32x32(ts + ch * 32, r);
+                    ptx::tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        if (ch * 32 + i < valid) {
+                            mx = fmaxf(mx, __uint_as_float(r[i]));
+                        }
+                    }
+                }
+                // lazy reference maximum: rescale only when it grew by more than the threshold
+                const bool grow = (j == 0) || ((mx - m_ref) * c > RESCALE_THRESHOLD);
+                if (__any_sync(0xffffffffu, grow && j != 0)) {
+                    const float alpha = (grow && j != 0) ? ptx::ex2((m_ref - mx) * c) : 1.0f;
+                    l *= alpha;
+#pragma unroll 1
+                    for (int ch = 0; ch < 4; ++ch) {
+                        uint32_t r[32];
+                        ptx::tmem_ld_32x32(to + ch * 32, r);
+                        ptx::tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+                        }
+                        ptx::tmem_st_32x32(to + ch * 32, r);
+                    }
+                    ptx::tmem_st_wait();
+                }
+                if (grow) {
+                    m_ref = mx;
+                }
+                const float mc = m_ref * c;
+                // pass 2: P = exp2(S * c - m_ref * c), written over S as packed bf16
+#pragma unroll 1
+                for (int ch = 0; ch < 4; ++ch) {
+                    uint32_t r[32];
+                    ptx::tmem_ld_32x32(ts + ch * 32, r);
+                    ptx::tmem_ld_wait();
+                    uint32_t pk[16];
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        float e0 = ptx::ex2(fmaf(__uint_as_float(r[2 * i]), c, -mc));
+                        float e1 = ptx::ex2(fmaf(__uint_as_float(r[2 * i + 1]), c, -mc));
+                        if (ch * 32 + 2 * i >= valid) {
+                            e0 = 0.0f;
+                        }
+                        if (ch * 32 + 2 * i + 1 >= valid) {
+                            e1 = 0.0f;
+                        }
+                        l += e0 + e1;
+                        pk[i] = ptx::pack_bf16x2(e0, e1);
+                    }
+                    ptx::tmem_st_32x16(ts + ch * 16, pk);
+                }
+                ptx::tmem_st_wait();
+                ptx::tc_fence_before();
+                ptx::mbar_arrive(&bar.p_ready[t]);
+            }
+            if (!ok) {
+                break;
+            }
+            // epilogue: O / l -> bf16, log-sum-exp
+            if (!ptx::mbar_wait(&bar.o_final[t], wc & 1u)) {
+                flag(p, ERR_SOFTMAX);
+                break;
+            }
+            ptx::tc_fence_after();
+            const float    inv    = 1.0f / l;
+            const bool     row_ok = row < p.Sq;
+            __nv_bfloat16* dst    = p.o + b * p.o_batch + static_cast<int64_t>(row) * p.o_row + h * p.o_head;
+#pragma unroll 1
+            for (int ch = 0; ch < 4; ++ch) {
+                uint32_t r[32];
+                ptx::tmem_ld_32x32(to + ch * 32, r);
+                ptx::tmem_ld_wait();
+                if (row_ok) {
+                    uint32_t pk[16];
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        pk[i] = ptx::pack_bf16x2(__uint_as_float(r[2 * i]) * inv, __uint_as_float(r[2 * i + 1]) * inv);
+                    }
+                    uint4* out = reinterpret_cast<uint4*>(dst + ch * 32);
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; ++q4) {
+                        out[q4] = make_uint4(pk[4 * q4], pk[4 * q4 + 1], pk[4 * q4 + 2], pk[4 * q4 + 3]);
+                    }
+                }
+            }
+            if (row_ok && p.lse) {
+                p.lse[(static_cast<int64_t>(b) * p.H + h) * p.Sq + row] = (m_ref * c + ptx::lg2(l)) * 0.6931471805599453f;
+            }
+            ptx::tc_fence_before();
+            ptx::mbar_arrive(&bar.o_free[t]);
+        }
+    }
+
+    ptx::tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        ptx::tmem_dealloc<512>(tmem);
+    }
+}
+
+}  // namespace
+
+extern "C" int fu_fmha_fwd(const FuFmhaArgs* a, void* stream)
+{
+    if (!a || !a->q || !a->k || !a->v || !a->o) {
+        return fu::fail(FU_E_ARG, "fu_fmha_fwd: null operand");
+    }
+    if (a->head_dim != D) {
+        return fu::fail(FU_E_UNSUPPORTED, "fu_fmha_fwd: head_dim %d (only 128 is built)", a->head_dim);
+    }
+    if (a->batch < 1 || a->heads < 1 || a->seq_q < 1 || a->seq_kv < 1) {
+        return fu::fail(FU_E_ARG, "fu_fmha_fwd: empty problem");
+    }
+    if ((reinterpret_cast<uintptr_t>(a->o) & 15u) || (a->o_row % 8) || (a->o_head % 8) || (a->o_batch % 8)) {
+        return fu::fail(FU_E_ARG, "fu_fmha_fwd: o needs 16-byte aligned rows");
+    }
+    Params p{};
+    int    rc = make_map_bshd(&p.map_q, a->q, a->batch, a->seq_q, a->heads, a->q_row, a->q_head, a->q_batch, BM);
+    if (rc == FU_OK) {
+        rc = make_map_bshd(&p.map_k, a->k, a->batch, a->seq_kv, a->heads, a->k_row, a->k_head, a->k_batch, BN);
+    }
+    if (rc == FU_OK) {
+        rc = make_map_bshd(&p.map_v, a->v, a->batch, a->seq_kv, a->heads, a->v_row, a->v_head, a->v_batch, BN);
+    }
+    if (rc != FU_OK) {
+        return rc;
+    }
+    p.o          = static_cast<__nv_bfloat16*>(a->o);
+    p.lse        = a->lse;
+    p.o_row      = a->o_row;
+    p.o_head     = a->o_head;
+    p.o_batch    = a->o_batch;
+    p.B          = a->batch;
+    p.H          = a->heads;
+    p.Sq         = a->seq_q;
+    p.Skv        = a->seq_kv;
+    p.q_blocks   = (a->seq_q + QT * BM - 1) / (QT * BM);
+    p.total_work = p.q_blocks * p.H * p.B;
+    p.n_kv       = (a->seq_kv + BN - 1) / BN;
+    p.scale      = a->scale;
+    p.scale_log2 = a->scale * 1.4426950408889634f;
+    p.err        = a->err;
+
+    int dev = 0, sms = 0;
+    FU_CUDA_OK(cudaGetDevice(&dev));
+    FU_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    static bool configured[64] = {};
+    if (dev < 64 && !configured[dev]) {
+        FU_CUDA_OK(cudaFuncSetAttribute(fmha_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        configured[dev] = true;
+    }
+    int grid = a->ctas > 0 ? std::min(a->ctas, sms) : sms;
+    grid     = std::max(1, std::min(grid, p.total_work));
+    fmha_fwd_kernel<<<grid, THREADS, SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(p);
+    FU_CUDA_OK(cudaGetLastError());
+    return FU_OK;
+}

@@ -59,6 +59,8 @@ enum {
     FU_A2A_EARLY_PUBLISH = 4,   // TEST ONLY negative control: announce completion before the payload
     FU_A2A_LDST          = 8,   // move data with 16-byte ld/st instead of bulk (TMA) copies
     FU_A2A_MUTE          = 16,  // TEST ONLY: never announce anything, so that peers' waits run out
+    FU_A2A_MINOR_SHARE   = 32,  // this launch may run beside another collective of the same rank on
+                                // an unordered stream: take a third of the device, not two thirds
 };
 
 typedef struct FuA2AArgs {
@@ -131,6 +133,61 @@ typedef struct FuQkvArgs {
     uint32_t*    err;
 } FuQkvArgs;
 FU_API int fu_qkv_rope_scatter(const FuQkvArgs* args, void* stream);
+
+// Fused mode-1 path: C[m, n] = A[m, :] * W[n, :]^T + bias + residual where A is the attention output
+// gathered from its owners: A[m, head*128 + x] = O_owner(head)[batch, seq_off + s, local head, x].
+// Every rank's O buffer has layout (b, s_total, head_splits[p], 128) bf16. `gather` is local scratch
+// of m x (heads*128) bf16 and `ready` of ceil(m/128)*world uint32 (zeroed by the launcher).
+typedef struct FuPullArgs {
+    const void*  w;
+    void*        c;
+    int64_t      m, n, ldw, ldc;
+    const float* bias;
+    const void*  residual;
+    int64_t      s_local, seq_off, s_total;
+    int32_t      rank, world;
+    int32_t      head_splits[FU_MAX_WORLD];
+    const void*  peer_o[FU_MAX_WORLD];
+    FuCtrl*      peer_ctrl[FU_MAX_WORLD];
+    void*        gather;
+    uint32_t*    ready;
+    int32_t      flags;
+    uint32_t     timeout_ms;
+    int32_t      ctas;
+    int32_t      pad_;
+    uint32_t*    err;
+} FuPullArgs;
+FU_API int fu_pull_outproj(const FuPullArgs* args, void* stream);
+
+// ---- flash attention (head_dim 128, non-causal, bf16) -----------------------------------------------
+// q, k, v, o are addressed as (batch, seq, head, 128) with explicit element strides for the seq, head
+// and batch axes, so both the window layout (b, s, h, d) and (b, h, s, d) work without a copy.
+// lse (nullable) is (batch, heads, seq_q) fp32, natural log. do/dq/dk/dv follow the layout of
+// o/q/k/v respectively; delta and dq_acc are scratch the caller provides for the backward.
+typedef struct FuFmhaArgs {
+    const void* q;
+    const void* k;
+    const void* v;
+    void*       o;
+    float*      lse;
+    int32_t     batch, heads, seq_q, seq_kv, head_dim;
+    float       scale;
+    int64_t     q_row, q_head, q_batch;
+    int64_t     k_row, k_head, k_batch;
+    int64_t     v_row, v_head, v_batch;
+    int64_t     o_row, o_head, o_batch;
+    int32_t     ctas;
+    int32_t     pad_;
+    uint32_t*   err;
+    // backward only
+    const void* d_o;
+    void*       dq;
+    void*       dk;
+    void*       dv;
+    float*      delta;   // (batch, heads, seq_q) fp32 scratch
+    float*      dq_acc;  // (batch, seq_q, heads, 128) fp32 scratch, zeroed by the launcher
+} FuFmhaArgs;
+FU_API int fu_fmha_fwd(const FuFmhaArgs* args, void* stream);
 
 FU_API const char* fu_last_error(void);
 FU_API const char* fu_build_info(void);  // "sm_100a;<nvcc version>;<library version>"

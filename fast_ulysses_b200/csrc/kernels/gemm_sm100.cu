@@ -284,6 +284,149 @@ __global__ void __launch_bounds__(THREADS, 1) qkv_rope_scatter_kernel(const __gr
     run(a.core, epi);
 }
 
+// ---- fused mode-1 path: pull attention output from peers, feed the output projection -----------------
+// A[m, head*128 + x] = O_owner(head)[batch, seq_off + s, local head, x]. Four extra warps per CTA
+// copy (M-tile, peer) blocks from the peers' O buffers into a local gather buffer with plain
+// loads over NVLink and publish a flag per block; the TMA producer of whichever CTA needs that
+// part of A waits for the flag (bounded) and then loads it from local memory, so every remote byte
+// crosses NVLink once and the transfer overlaps the GEMM tile by tile. No multicast anywhere.
+struct PullParams {
+    const uint8_t* peer_o[FU_MAX_WORLD];
+    Peers          peers;
+    uint8_t*       gather;   // (M, heads_total * 128) bf16, local
+    uint32_t*      ready;    // [tiles_m * world], zero before launch
+    int            M, tiles_m, heads_total;
+    int64_t        s_local, seq_off, s_total;
+    uint8_t        heads_of[FU_MAX_WORLD];
+    uint16_t       head_start[FU_MAX_WORLD];
+    uint8_t        owner[MAX_HEADS];
+    int            handshake;
+    uint32_t*      err;
+};
+
+struct PullSrc {
+    const PullParams& p;
+    int               seen_mt, seen_peer;
+    __device__ explicit PullSrc(const PullParams& params) : p(params), seen_mt(-1), seen_peer(-1) {}
+
+    __device__ bool ready(int mt, int kb)
+    {
+        const int peer = p.owner[kb >> 1];  // BK = 64: two K-blocks per head
+        if (mt == seen_mt && peer == seen_peer) {
+            return true;
+        }
+        const uint32_t* f  = p.ready + mt * p.peers.world + peer;
+        const uint64_t  t0 = ptx::globaltimer_ns();
+        uint32_t        spins = 0;
+        while (ptx::ld_acquire_gpu_u32(f) == 0u) {
+            if ((++spins & 255u) == 0u && ptx::globaltimer_ns() - t0 > p.peers.timeout_ns) {
+                return false;
+            }
+        }
+        ptx::fence_proxy_async();  // generic-proxy writes by the pullers -> TMA reads below
+        seen_mt   = mt;
+        seen_peer = peer;
+        return true;
+    }
+};
+
+struct PullAux {
+    static constexpr int kWarps = 4;
+    const PullParams&    p;
+    __device__ explicit PullAux(const PullParams& params) : p(params) {}
+
+    __device__ static void aux_barrier() { asm volatile("bar.sync 2, 128;" ::: "memory"); }
+
+    __device__ void run(int aux_warp, int lane) const
+    {
+        __shared__ uint32_t ticket;
+        const Peers&   peers = p.peers;
+        const int      tid   = aux_warp * 32 + lane;
+        const uint64_t base  = *reinterpret_cast<volatile uint64_t*>(&peers.own->epoch);
+        // Opening: every rank says "my attention output is complete" (stream order put this kernel
+        // after its attention kernel) and nobody reads a peer before that.
+        if (p.handshake && aux_warp == 0) {
+            if (blockIdx.x == 0) {
+                hs_announce(peers, base + 1);
+            }
+            hs_await(peers, base + 1, FU_ST_OPEN_TIMEOUT);
+        }
+        aux_barrier();
+        const int units = p.tiles_m * peers.world;
+        for (int u = blockIdx.x; u < units; u += gridDim.x) {
+            const int mt   = u / peers.world;
+            const int peer = (peers.rank + (u - mt * peers.world)) % peers.world;
+            const int rows = min(BM, p.M - mt * BM);
+            const uint32_t vpr  = static_cast<uint32_t>(p.heads_of[peer]) * 16u;  // 16-byte vectors per row
+            const uint32_t nvec = vpr * rows;
+            const uint8_t* src  = p.peer_o[peer];
+            const int64_t  src_pitch = static_cast<int64_t>(p.heads_of[peer]) * 256;
+            const int64_t  dst_pitch = static_cast<int64_t>(p.heads_total) * 256;
+            uint8_t*       dst  = p.gather + static_cast<int64_t>(p.head_start[peer]) * 256;
+            for (uint32_t v0 = tid; v0 < nvec; v0 += 8 * 128) {
+                uint4    val[8];
+                uint8_t* to[8];
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    const uint32_t v = v0 + k * 128;
+                    if (v < nvec) {
+                        const uint32_t r     = v / vpr;
+                        const uint32_t c     = v - r * vpr;
+                        const int64_t  row   = static_cast<int64_t>(mt) * BM + r;
+                        const int64_t  batch = row / p.s_local;
+                        const int64_t  s     = row - batch * p.s_local;
+                        val[k] = ptx::ld_v4(src + (batch * p.s_total + p.seq_off + s) * src_pitch + (c << 4));
+                        to[k]  = dst + row * dst_pitch + (c << 4);
+                    }
+                }
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    if (v0 + k * 128 < nvec) {
+                        ptx::st_v4(to[k], val[k]);
+                    }
+                }
+            }
+            __threadfence();
+            aux_barrier();
+            if (tid == 0) {
+                asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p.ready + mt * peers.world + peer), "r"(1u)
+                             : "memory");
+            }
+        }
+        // Closing: "I have finished reading everybody's output", so that the owners may overwrite
+        // it; the last CTA also waits for the same word from all peers before the kernel ends.
+        aux_barrier();
+        if (tid == 0) {
+            ticket = atomicAdd(&peers.own->arrive[0], 1u);
+        }
+        aux_barrier();
+        if (ticket == gridDim.x - 1 && aux_warp == 0) {
+            if (p.handshake) {
+                ptx::fence_sys();
+                hs_announce(peers, base + 2);
+                hs_await(peers, base + 2, FU_ST_CLOSE_TIMEOUT);
+            }
+            if (lane == 0) {
+                peers.own->arrive[0] = 0;
+                __threadfence();
+                *reinterpret_cast<volatile uint64_t*>(&peers.own->epoch) = base + 2;
+            }
+        }
+    }
+};
+
+struct PullArgs {
+    Core       core;
+    PlainEpi   epi;
+    PullParams pull;
+};
+
+__global__ void __launch_bounds__(THREADS + 128, 1) pull_outproj_kernel(const __grid_constant__ PullArgs a)
+{
+    PlainEpi epi = a.epi;
+    run(a.core, epi, PullSrc(a.pull), PullAux(a.pull));
+}
+
 int launch_grid(int ctas, int tiles)
 {
     int dev = 0, sms = 0;
@@ -431,6 +574,79 @@ extern "C" int fu_qkv_rope_scatter(const FuQkvArgs* q, void* stream)
     }
     const int grid = launch_grid(q->ctas, a.core.tiles_m * a.core.tiles_n);
     qkv_rope_scatter_kernel<<<grid, THREADS, SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(a);
+    FU_CUDA_OK(cudaGetLastError());
+    return FU_OK;
+}
+
+extern "C" int fu_pull_outproj(const FuPullArgs* q, void* stream_v)
+{
+    if (!q || !q->w || !q->c || !q->gather || !q->ready) {
+        return fu::fail(FU_E_ARG, "fu_pull_outproj: null operand");
+    }
+    if (q->world < 1 || q->world > FU_MAX_WORLD || q->rank < 0 || q->rank >= q->world) {
+        return fu::fail(FU_E_ARG, "fu_pull_outproj: rank %d / world %d", q->rank, q->world);
+    }
+    if (q->s_local <= 0 || q->m % q->s_local) {
+        return fu::fail(FU_E_ARG, "fu_pull_outproj: m=%lld is not a multiple of s_local=%lld", (long long)q->m,
+                        (long long)q->s_local);
+    }
+    if ((q->ldc % 8) || (reinterpret_cast<uintptr_t>(q->c) & 15u)) {
+        return fu::fail(FU_E_ARG, "fu_pull_outproj: C needs 16-byte aligned rows");
+    }
+    PullArgs a{};
+    PullParams& e = a.pull;
+    int heads = 0;
+    for (int p = 0; p < q->world; ++p) {
+        if (q->head_splits[p] < 0 || q->head_splits[p] > 255 || !q->peer_o[p] || !q->peer_ctrl[p]) {
+            return fu::fail(FU_E_ARG, "fu_pull_outproj: bad shard or missing buffer for rank %d", p);
+        }
+        e.heads_of[p]   = static_cast<uint8_t>(q->head_splits[p]);
+        e.head_start[p] = static_cast<uint16_t>(heads);
+        for (int i = 0; i < q->head_splits[p]; ++i, ++heads) {
+            if (heads >= MAX_HEADS) {
+                return fu::fail(FU_E_ARG, "fu_pull_outproj: too many heads");
+            }
+            e.owner[heads] = static_cast<uint8_t>(p);
+        }
+        e.peer_o[p]     = static_cast<const uint8_t*>(q->peer_o[p]);
+        e.peers.ctrl[p] = q->peer_ctrl[p];
+    }
+    const int64_t k = static_cast<int64_t>(heads) * HEAD_DIM;
+    int rc = fill_core(a.core, q->gather, q->w, q->m, q->n, k, k, q->ldw, q->err);
+    if (rc != FU_OK) {
+        return rc;
+    }
+    e.peers.own        = q->peer_ctrl[q->rank];
+    e.peers.rank       = q->rank;
+    e.peers.world      = q->world;
+    e.peers.mute       = (q->flags & FU_A2A_MUTE) ? 1 : 0;
+    e.peers.timeout_ns = static_cast<uint64_t>(q->timeout_ms ? q->timeout_ms : 10000) * 1000000ull;
+    e.handshake        = (q->flags & FU_A2A_NO_HANDSHAKE) ? 0 : 1;
+    e.gather           = static_cast<uint8_t*>(q->gather);
+    e.ready            = q->ready;
+    e.M                = a.core.M;
+    e.tiles_m          = a.core.tiles_m;
+    e.heads_total      = heads;
+    e.s_local          = q->s_local;
+    e.seq_off          = q->seq_off;
+    e.s_total          = q->s_total;
+    e.err              = q->err;
+    a.epi.c            = static_cast<__nv_bfloat16*>(q->c);
+    a.epi.residual     = static_cast<const __nv_bfloat16*>(q->residual);
+    a.epi.bias         = q->bias;
+    a.epi.ldc          = q->ldc;
+    a.epi.M            = a.core.M;
+    a.epi.N            = a.core.N;
+    a.epi.act          = 0;
+    rc                 = set_smem(pull_outproj_kernel);
+    if (rc != FU_OK) {
+        return rc;
+    }
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    FU_CUDA_OK(cudaMemsetAsync(q->ready, 0, sizeof(uint32_t) * a.core.tiles_m * q->world, stream));
+    // One CTA per SM and never more than the SM count: CTAs wait on flags other CTAs publish.
+    const int grid = launch_grid(q->ctas, 1 << 30);
+    pull_outproj_kernel<<<grid, THREADS + 128, SMEM_BYTES, stream>>>(a);
     FU_CUDA_OK(cudaGetLastError());
     return FU_OK;
 }

@@ -69,12 +69,24 @@ __device__ __forceinline__ void flag_error(const Core& c, uint32_t code)
     }
 }
 
+// Optional policies. `Src::ready(mt, kb)` runs in the producer thread before the loads of K-block
+// `kb` of M-tile `mt` are issued and may wait (bounded) for that part of A to exist; it returns
+// false to give up. `Aux::run(aux_warp, lane)` is executed by `Aux::kWarps` extra warps (warps 6..)
+// alongside the GEMM, e.g. to pull A from peers' memory into the buffer the GEMM reads.
+struct NoSrc {
+    __device__ __forceinline__ bool ready(int, int) const { return true; }
+};
+struct NoAux {
+    static constexpr int kWarps = 0;
+    __device__ __forceinline__ void run(int, int) const {}
+};
+
 // Epi requirements:
 //   __device__ void open(int epi_warp)                       once, before the first tile
 //   __device__ void tile(uint32_t tmem_acc, int mt, int nt, int quarter, int lane)
 //   __device__ void close(int epi_tid)                       once, after the last tile (all 128 threads)
-template <class Epi>
-__device__ __forceinline__ void run(const Core& core, Epi& epi)
+template <class Epi, class Src = NoSrc, class Aux = NoAux>
+__device__ __forceinline__ void run(const Core& core, Epi& epi, Src src = Src{}, Aux aux = Aux{})
 {
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t       full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2];
@@ -119,7 +131,7 @@ __device__ __forceinline__ void run(const Core& core, Epi& epi)
                 for (int kb = 0; kb < kblocks; ++kb, ++it) {
                     const int      s      = it % STAGES;
                     const uint32_t parity = ((it / STAGES) & 1u) ^ 1u;
-                    if (!ptx::mbar_wait(&empty[s], parity)) {
+                    if (!ptx::mbar_wait(&empty[s], parity) || !src.ready(mt, kb)) {
                         flag_error(core, ERR_PRODUCER_WAIT);
                         ok = false;
                         break;
@@ -174,6 +186,9 @@ __device__ __forceinline__ void run(const Core& core, Epi& epi)
             }
         }
         __syncwarp();
+    }
+    else if (warp >= 6) {
+        aux.run(warp - 6, lane);
     }
     else {
         const int epi_warp = warp - 2;

@@ -86,4 +86,30 @@ inline int make_map_3d(CUtensorMap* map, const void* base, int elem_bytes, uint6
     return FU_OK;
 }
 
+// A (batch, rows, heads, 128) bf16 tensor such as q/k/v/o in the window layout, addressed as
+// (x, row, head, batch) and read in boxes of `box_rows` rows x 64 columns of one head.
+inline int make_map_bshd(CUtensorMap* map, const void* base, uint64_t batch, uint64_t rows, uint64_t heads,
+                         uint64_t row_pitch, uint64_t head_pitch, uint64_t batch_pitch, uint32_t box_rows)
+{
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) {
+        return fail(FU_E_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    }
+    if ((reinterpret_cast<uintptr_t>(base) & 15u) || ((row_pitch * 2) & 15u) || ((head_pitch * 2) & 15u)
+        || ((batch_pitch * 2) & 15u)) {
+        return fail(FU_E_ARG, "a TMA operand needs 16-byte aligned base and pitches");
+    }
+    const cuuint64_t dims[4]    = {128, rows, heads, batch};
+    const cuuint64_t strides[3] = {row_pitch * 2, head_pitch * 2, batch_pitch * 2};
+    const cuuint32_t box[4]     = {64, box_rows, 1, 1};
+    const cuuint32_t estr[4]    = {1, 1, 1, 1};
+    const CUresult   rc = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (rc != CUDA_SUCCESS) {
+        return fail(FU_E_CUDA, "cuTensorMapEncodeTiled (bshd) failed with %d", static_cast<int>(rc));
+    }
+    return FU_OK;
+}
+
 }  // namespace fu

@@ -281,7 +281,7 @@ at::Tensor run_async(Group& g, const at::Tensor& input, int64_t mode, const Spli
     cuda_ok(cudaStreamWaitEvent(comm.stream(), ready, 0), "cudaStreamWaitEvent");
     cuda_ok(cudaEventDestroy(ready), "cudaEventDestroy");
     c10::cuda::CUDACachingAllocator::recordStream(p.x.storage().data_ptr(), comm);
-    run_prepared(g, p, comm.stream(), 0);
+    run_prepared(g, p, comm.stream(), FU_A2A_MINOR_SHARE);
     return p.output;
 }
 

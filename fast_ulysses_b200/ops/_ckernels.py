@@ -18,6 +18,7 @@ FU_A2A_STAMPS = 2
 FU_A2A_EARLY_PUBLISH = 4
 FU_A2A_LDST = 8
 FU_A2A_MUTE = 16
+FU_A2A_MINOR_SHARE = 32
 
 
 class FuRoute(C.Structure):
@@ -51,7 +52,7 @@ def lib() -> C.CDLL:
         _lib.fu_build_info.restype = C.c_char_p
         _lib.fu_a2a4d.argtypes = [C.POINTER(FuA2AArgs), C.c_void_p]
         _lib.fu_a2a4d.restype = C.c_int
-        for name in ("fu_gemm_bf16", "fu_qkv_rope_scatter"):
+        for name in ("fu_gemm_bf16", "fu_qkv_rope_scatter", "fu_fmha_fwd", "fu_pull_outproj"):
             getattr(_lib, name).restype = C.c_int
             getattr(_lib, name).argtypes = [C.c_void_p, C.c_void_p]
     return _lib
@@ -89,3 +90,26 @@ def stream_ptr():
     import torch
 
     return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+class FuFmhaArgs(C.Structure):
+    _fields_ = [("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("o", C.c_void_p), ("lse", C.c_void_p),
+                ("batch", C.c_int32), ("heads", C.c_int32), ("seq_q", C.c_int32), ("seq_kv", C.c_int32),
+                ("head_dim", C.c_int32), ("scale", C.c_float),
+                ("q_row", C.c_int64), ("q_head", C.c_int64), ("q_batch", C.c_int64),
+                ("k_row", C.c_int64), ("k_head", C.c_int64), ("k_batch", C.c_int64),
+                ("v_row", C.c_int64), ("v_head", C.c_int64), ("v_batch", C.c_int64),
+                ("o_row", C.c_int64), ("o_head", C.c_int64), ("o_batch", C.c_int64),
+                ("ctas", C.c_int32), ("pad_", C.c_int32), ("err", C.c_void_p),
+                ("d_o", C.c_void_p), ("dq", C.c_void_p), ("dk", C.c_void_p), ("dv", C.c_void_p),
+                ("delta", C.c_void_p), ("dq_acc", C.c_void_p)]
+
+
+class FuPullArgs(C.Structure):
+    _fields_ = [("w", C.c_void_p), ("c", C.c_void_p), ("m", C.c_int64), ("n", C.c_int64), ("ldw", C.c_int64),
+                ("ldc", C.c_int64), ("bias", C.c_void_p), ("residual", C.c_void_p), ("s_local", C.c_int64),
+                ("seq_off", C.c_int64), ("s_total", C.c_int64), ("rank", C.c_int32), ("world", C.c_int32),
+                ("head_splits", C.c_int32 * FU_MAX_WORLD), ("peer_o", C.c_void_p * FU_MAX_WORLD),
+                ("peer_ctrl", C.c_void_p * FU_MAX_WORLD), ("gather", C.c_void_p), ("ready", C.c_void_p),
+                ("flags", C.c_int32), ("timeout_ms", C.c_uint32), ("ctas", C.c_int32), ("pad_", C.c_int32),
+                ("err", C.c_void_p)]

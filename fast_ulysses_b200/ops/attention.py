@@ -1,0 +1,57 @@
+"""Flash attention on the tcgen05 tensor cores (csrc/kernels/fmha_fwd_sm100.cu, fmha_bwd_sm100.cu).
+
+Tensors use the ``(batch, seq, heads, 128)`` layout of the all-to-all windows; any view whose last
+axis is contiguous and whose other strides are multiples of 8 elements is read in place.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+import math
+
+import torch
+
+from . import _ckernels as ck
+from .gemm import error_word
+
+
+def _strides(t: torch.Tensor):
+    assert t.dim() == 4 and t.shape[-1] == 128 and t.stride(3) == 1 and t.dtype == torch.bfloat16, (t.shape, t.stride())
+    return t.stride(1), t.stride(2), t.stride(0)
+
+
+def _fill(a, q, k, v, o):
+    b, sq, h, _ = q.shape
+    a.q, a.k, a.v, a.o = q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr()
+    a.batch, a.heads, a.seq_q, a.seq_kv, a.head_dim = b, h, sq, k.shape[1], 128
+    a.q_row, a.q_head, a.q_batch = _strides(q)
+    a.k_row, a.k_head, a.k_batch = _strides(k)
+    a.v_row, a.v_head, a.v_batch = _strides(v)
+    a.o_row, a.o_head, a.o_batch = _strides(o)
+    a.err = error_word(q.device).data_ptr()
+
+
+def fmha_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scale: float | None = None,
+             out: torch.Tensor | None = None, ctas: int = 0):
+    """``softmax(q k^T * scale) v`` for (b, s, h, 128) bf16 tensors. Returns ``(o, lse)`` with
+    ``lse`` of shape (b, h, s_q), fp32, natural log."""
+    b, sq, h, d = q.shape
+    assert k.shape == v.shape and k.shape[0] == b and k.shape[2] == h and d == 128
+    o = out if out is not None else torch.empty(b, sq, h, d, dtype=torch.bfloat16, device=q.device)
+    lse = torch.empty(b, h, sq, dtype=torch.float32, device=q.device)
+    a = ck.FuFmhaArgs()
+    _fill(a, q, k, v, o)
+    a.lse = lse.data_ptr()
+    a.scale = scale if scale is not None else 1.0 / math.sqrt(d)
+    a.ctas = ctas
+    ck.check(ck.lib().fu_fmha_fwd(C.byref(a), ck.stream_ptr()))
+    return o, lse
+
+
+def attention_reference(q, k, v, scale=None):
+    """fp32 PyTorch statement on (b, s, h, d) tensors; returns (o, lse)."""
+    scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
+    s = torch.einsum("bqhd,bkhd->bhqk", q.float(), k.float()) * scale
+    lse = torch.logsumexp(s, dim=-1)
+    o = torch.einsum("bhqk,bkhd->bqhd", torch.softmax(s, dim=-1), v.float())
+    return o, lse
