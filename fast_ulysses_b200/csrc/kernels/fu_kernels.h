@@ -184,10 +184,12 @@ typedef struct FuFmhaArgs {
     void*       dq;
     void*       dk;
     void*       dv;
-    float*      delta;   // (batch, heads, seq_q) fp32 scratch
+    float*      delta;   // fp32 scratch of 2 * batch * heads * roundup(seq_q, 128) floats
     float*      dq_acc;  // (batch, seq_q, heads, 128) fp32 scratch, zeroed by the launcher
 } FuFmhaArgs;
 FU_API int fu_fmha_fwd(const FuFmhaArgs* args, void* stream);
+// d_o is addressed with o's strides, dq / dk / dv with q's / k's / v's strides.
+FU_API int fu_fmha_bwd(const FuFmhaArgs* args, void* stream);
 
 FU_API const char* fu_last_error(void);
 FU_API const char* fu_build_info(void);  // "sm_100a;<nvcc version>;<library version>"

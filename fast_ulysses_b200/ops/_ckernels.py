@@ -52,7 +52,7 @@ def lib() -> C.CDLL:
         _lib.fu_build_info.restype = C.c_char_p
         _lib.fu_a2a4d.argtypes = [C.POINTER(FuA2AArgs), C.c_void_p]
         _lib.fu_a2a4d.restype = C.c_int
-        for name in ("fu_gemm_bf16", "fu_qkv_rope_scatter", "fu_fmha_fwd", "fu_pull_outproj"):
+        for name in ("fu_gemm_bf16", "fu_qkv_rope_scatter", "fu_fmha_fwd", "fu_fmha_bwd", "fu_pull_outproj"):
             getattr(_lib, name).restype = C.c_int
             getattr(_lib, name).argtypes = [C.c_void_p, C.c_void_p]
     return _lib

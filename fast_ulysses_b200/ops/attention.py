@@ -55,3 +55,49 @@ def attention_reference(q, k, v, scale=None):
     lse = torch.logsumexp(s, dim=-1)
     o = torch.einsum("bhqk,bkhd->bqhd", torch.softmax(s, dim=-1), v.float())
     return o, lse
+
+
+def fmha_bwd(q, k, v, o, lse, d_o, *, scale: float | None = None, ctas: int = 0):
+    """Gradients of ``fmha_fwd``. All tensors (b, s, h, 128) bf16; ``d_o`` must share ``o``'s
+    strides. Returns ``(dq, dk, dv)`` shaped and strided like q, k, v (dense)."""
+    b, sq, h, d = q.shape
+    if d_o.stride() != o.stride():
+        d_o = d_o.contiguous()
+        o = o.contiguous()
+    dq = torch.empty(b, sq, h, d, dtype=torch.bfloat16, device=q.device)
+    dk = torch.empty(b, k.shape[1], h, d, dtype=torch.bfloat16, device=q.device)
+    dv = torch.empty_like(dk)
+    # the launcher addresses dq/dk/dv with the strides of q/k/v: hand it dense q/k/v views
+    qc, kc, vc = (t if t.is_contiguous() else t.contiguous() for t in (q, k, v))
+    sq_pad = (sq + 127) // 128 * 128
+    stats = torch.empty(2 * b * h * sq_pad, dtype=torch.float32, device=q.device)
+    dq_acc = torch.empty(b, sq, h, d, dtype=torch.float32, device=q.device)
+    a = ck.FuFmhaArgs()
+    _fill(a, qc, kc, vc, o)
+    a.lse = lse.data_ptr()
+    a.scale = scale if scale is not None else 1.0 / math.sqrt(d)
+    a.ctas = ctas
+    a.d_o, a.dq, a.dk, a.dv = d_o.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
+    a.delta, a.dq_acc = stats.data_ptr(), dq_acc.data_ptr()
+    ck.check(ck.lib().fu_fmha_bwd(C.byref(a), ck.stream_ptr()))
+    return dq, dk, dv
+
+
+class _Attention(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, scale):
+        o, lse = fmha_fwd(q, k, v, scale=scale)
+        ctx.save_for_backward(q, k, v, o, lse)
+        ctx.scale = scale
+        return o
+
+    @staticmethod
+    def backward(ctx, d_o):
+        q, k, v, o, lse = ctx.saved_tensors
+        dq, dk, dv = fmha_bwd(q, k, v, o, lse, d_o.contiguous() if not d_o.is_contiguous() else d_o, scale=ctx.scale)
+        return dq, dk, dv, None
+
+
+def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float | None = None) -> torch.Tensor:
+    """Differentiable non-causal attention on (b, s, h, 128) bf16 tensors (tcgen05 fwd and bwd)."""
+    return _Attention.apply(q, k, v, scale)

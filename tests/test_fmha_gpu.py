@@ -60,3 +60,36 @@ def test_against_sdpa_longer_sequence():
     gemm.check_errors()
     ref = torch.nn.functional.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2))
     assert rel_err(o, ref.transpose(1, 2)) < 1.5e-2
+
+
+@pytest.mark.parametrize("b,h,sq,skv", [(1, 1, 128, 128), (1, 2, 256, 384), (2, 2, 300, 500), (1, 1, 1000, 777)])
+def test_backward_matches_fp32_autograd(b, h, sq, skv):
+    torch.manual_seed(sq * 3 + skv)
+    q = torch.randn(b, sq, h, 128, device="cuda").bfloat16().requires_grad_()
+    k = torch.randn(b, skv, h, 128, device="cuda").bfloat16().requires_grad_()
+    v = torch.randn(b, skv, h, 128, device="cuda").bfloat16().requires_grad_()
+    o = attention.attention(q, k, v)
+    d_o = torch.randn_like(o)
+    o.backward(d_o)
+    gemm.check_errors()
+    qr, kr, vr = (t.detach().float().requires_grad_() for t in (q, k, v))
+    o_ref, _ = attention.attention_reference(qr, kr, vr)
+    o_ref.backward(d_o.float())
+    assert rel_err(q.grad, qr.grad) < 2e-2, ("dq", rel_err(q.grad, qr.grad))
+    assert rel_err(k.grad, kr.grad) < 2e-2, ("dk", rel_err(k.grad, kr.grad))
+    assert rel_err(v.grad, vr.grad) < 2e-2, ("dv", rel_err(v.grad, vr.grad))
+
+
+def test_backward_many_blocks_per_cta():
+    torch.manual_seed(1)
+    q = torch.randn(1, 640, 3, 128, device="cuda").bfloat16()
+    k = torch.randn(1, 900, 3, 128, device="cuda").bfloat16()
+    v = torch.randn(1, 900, 3, 128, device="cuda").bfloat16()
+    o, lse = attention.fmha_fwd(q, k, v)
+    d_o = torch.randn_like(o)
+    dq, dk, dv = attention.fmha_bwd(q, k, v, o, lse, d_o, ctas=2)
+    gemm.check_errors()
+    qr, kr, vr = (t.float().requires_grad_() for t in (q, k, v))
+    o_ref, _ = attention.attention_reference(qr, kr, vr)
+    o_ref.backward(d_o.float())
+    assert rel_err(dq, qr.grad) < 2e-2 and rel_err(dk, kr.grad) < 2e-2 and rel_err(dv, vr.grad) < 2e-2
