@@ -287,20 +287,31 @@ __global__ void __launch_bounds__(THREADS, 1) fmha_fwd_kernel(const __grid_const
                 }
                 ptx::tc_fence_after();
                 const int valid = min(BN, p.Skv - j * BN);  // columns of this step that exist
-                // pass 1: row maximum
-                float mx = -INFINITY;
-#pragma unroll 1
-                for (int ch = 0; ch < 4; ++ch) {
-                    uint32_t r[32];
-                    ptx::tmem_ld_32x32(ts + ch * 32, r);
-                    ptx::tmem_ld_wait();
+                // The whole row of S in registers with a single wait: the softmax sits on the
+                // critical path between two MMAs, so its latency matters more than its register use.
+                uint32_t r[BN];
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        if (ch * 32 + i < valid) {
-                            mx = fmaxf(mx, __uint_as_float(r[i]));
+                for (int ch = 0; ch < 4; ++ch) {
+                    ptx::tmem_ld_32x32(ts + ch * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[ch * 32]));
+                }
+                ptx::tmem_ld_wait();
+                if (valid < BN) {
+#pragma unroll
+                    for (int i = 0; i < BN; ++i) {
+                        if (i >= valid) {
+                            r[i] = 0xff800000u;  // -inf: exp2 gives exactly 0
                         }
                     }
                 }
+                float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+                for (int i = 0; i < BN; i += 4) {
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        mx4[u] = fmaxf(mx4[u], __uint_as_float(r[i + u]));
+                    }
+                }
+                const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
                 // lazy reference maximum: rescale only when it grew by more than the threshold
                 const bool grow = (j == 0) || ((mx - m_ref) * c > RESCALE_THRESHOLD);
                 if (__any_sync(0xffffffffu, grow && j != 0)) {
@@ -308,14 +319,14 @@ __global__ void __launch_bounds__(THREADS, 1) fmha_fwd_kernel(const __grid_const
                     l *= alpha;
 #pragma unroll 1
                     for (int ch = 0; ch < 4; ++ch) {
-                        uint32_t r[32];
-                        ptx::tmem_ld_32x32(to + ch * 32, r);
+                        uint32_t ro[32];
+                        ptx::tmem_ld_32x32(to + ch * 32, ro);
                         ptx::tmem_ld_wait();
 #pragma unroll
                         for (int i = 0; i < 32; ++i) {
-                            r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+                            ro[i] = __float_as_uint(__uint_as_float(ro[i]) * alpha);
                         }
-                        ptx::tmem_st_32x32(to + ch * 32, r);
+                        ptx::tmem_st_32x32(to + ch * 32, ro);
                     }
                     ptx::tmem_st_wait();
                 }
@@ -323,28 +334,21 @@ __global__ void __launch_bounds__(THREADS, 1) fmha_fwd_kernel(const __grid_const
                     m_ref = mx;
                 }
                 const float mc = m_ref * c;
-                // pass 2: P = exp2(S * c - m_ref * c), written over S as packed bf16
-#pragma unroll 1
+                // P = exp2(S * c - m_ref * c), written over S as packed bf16
+                float l4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
                 for (int ch = 0; ch < 4; ++ch) {
-                    uint32_t r[32];
-                    ptx::tmem_ld_32x32(ts + ch * 32, r);
-                    ptx::tmem_ld_wait();
                     uint32_t pk[16];
 #pragma unroll
                     for (int i = 0; i < 16; ++i) {
-                        float e0 = ptx::ex2(fmaf(__uint_as_float(r[2 * i]), c, -mc));
-                        float e1 = ptx::ex2(fmaf(__uint_as_float(r[2 * i + 1]), c, -mc));
-                        if (ch * 32 + 2 * i >= valid) {
-                            e0 = 0.0f;
-                        }
-                        if (ch * 32 + 2 * i + 1 >= valid) {
-                            e1 = 0.0f;
-                        }
-                        l += e0 + e1;
+                        const float e0 = ptx::ex2(fmaf(__uint_as_float(r[ch * 32 + 2 * i]), c, -mc));
+                        const float e1 = ptx::ex2(fmaf(__uint_as_float(r[ch * 32 + 2 * i + 1]), c, -mc));
+                        l4[i & 3] += e0 + e1;
                         pk[i] = ptx::pack_bf16x2(e0, e1);
                     }
                     ptx::tmem_st_32x16(ts + ch * 16, pk);
                 }
+                l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
                 ptx::tmem_st_wait();
                 ptx::tc_fence_before();
                 ptx::mbar_arrive(&bar.p_ready[t]);

@@ -131,8 +131,35 @@ typedef struct FuQkvArgs {
     uint32_t     timeout_ms;
     int32_t      ctas;
     uint32_t*    err;
+    // Generalisation (append-only). `n_types` projections share the head layout (3 = q, k, v;
+    // 1 = a single tensor, e.g. the gradient of the attention output on its way back to the head
+    // owners); the first `n_normed` of them get RMSNorm + RoPE. 0 / 0 means the default 3 / 2.
+    // `y_save` (nullable) receives the pre-norm values of the normed projections, row-major
+    // (m, n_normed * heads * 128) bf16 with leading dimension `ld_y`, for the backward pass.
+    int32_t      n_types, n_normed;
+    void*        y_save;
+    int64_t      ld_y;
 } FuQkvArgs;
 FU_API int fu_qkv_rope_scatter(const FuQkvArgs* args, void* stream);
+
+// Backward of per-head RMSNorm -> RoPE for q and k. dq, dk: (m, heads, 128) bf16 dense; y: the
+// pre-norm projections saved by fu_qkv_rope_scatter; dy receives d(projection) for q at column 0
+// and for k at column heads*128; dgamma_* (nullable, fp32[128]) are accumulated into.
+typedef struct FuNormRopeBwdArgs {
+    const void*  dq;
+    const void*  dk;
+    const void*  y;
+    void*        dy;
+    const float* rope;
+    const float* gamma_q;
+    const float* gamma_k;
+    float*       dgamma_q;
+    float*       dgamma_k;
+    int64_t      m, s_local, ld_y, ld_dy;
+    int32_t      heads;
+    float        eps;
+} FuNormRopeBwdArgs;
+FU_API int fu_qk_norm_rope_bwd(const FuNormRopeBwdArgs* args, void* stream);
 
 // Fused mode-1 path: C[m, n] = A[m, :] * W[n, :]^T + bias + residual where A is the attention output
 // gathered from its owners: A[m, head*128 + x] = O_owner(head)[batch, seq_off + s, local head, x].

@@ -149,6 +149,9 @@ struct QkvParams {
     uint8_t       local[MAX_HEADS];  // head -> index inside its owner's shard
     uint8_t       heads_of[FU_MAX_WORLD];
     int           handshake;
+    int           n_types, n_normed;
+    __nv_bfloat16* y_save;
+    int64_t       ld_y;
 };
 
 // The functor keeps a reference to the parameters (they stay in the kernel's constant bank) and
@@ -211,9 +214,10 @@ struct QkvEpi {
         for (int hh = 0; hh < BN / HEAD_DIM; ++hh) {
             const int head_global = nt * (BN / HEAD_DIM) + hh;
             const int type        = head_global / heads;  // 0 q, 1 k, 2 v
-            if (type > 2) {
+            if (type >= p.n_types) {
                 break;
             }
+            const bool normed = type < p.n_normed;
             const int      head  = head_global - type * heads;
             const int      peer  = p.owner[head];
             const int64_t  hp    = p.heads_of[peer];
@@ -221,7 +225,7 @@ struct QkvEpi {
                            + (((batch * s_total + seq_off + s) * hp + p.local[head]) * HEAD_DIM) * 2;
             const uint32_t tcol  = tmem_acc + hh * HEAD_DIM;
             float          scale = 1.0f;
-            if (type < 2) {
+            if (normed) {
                 float ss = 0.0f;
 #pragma unroll 1
                 for (int chunk = 0; chunk < 4; ++chunk) {
@@ -247,7 +251,18 @@ struct QkvEpi {
                     continue;
                 }
                 uint32_t o[16];
-                if (type < 2) {
+                if (normed) {
+                    if (p.y_save) {
+                        uint4* ys = reinterpret_cast<uint4*>(p.y_save + static_cast<int64_t>(row) * p.ld_y
+                                                             + head_global * HEAD_DIM + chunk * 32);
+#pragma unroll
+                        for (int q4 = 0; q4 < 4; ++q4) {
+                            ys[q4] = make_uint4(pack_bf16(__uint_as_float(r[8 * q4]), __uint_as_float(r[8 * q4 + 1])),
+                                                pack_bf16(__uint_as_float(r[8 * q4 + 2]), __uint_as_float(r[8 * q4 + 3])),
+                                                pack_bf16(__uint_as_float(r[8 * q4 + 4]), __uint_as_float(r[8 * q4 + 5])),
+                                                pack_bf16(__uint_as_float(r[8 * q4 + 6]), __uint_as_float(r[8 * q4 + 7])));
+                        }
+                    }
 #pragma unroll
                     for (int i = 0; i < 16; ++i) {
                         const int    c0 = chunk * 32 + 2 * i;
@@ -510,21 +525,30 @@ extern "C" int fu_gemm_bf16(const FuGemmArgs* g, void* stream)
 
 extern "C" int fu_qkv_rope_scatter(const FuQkvArgs* q, void* stream)
 {
-    if (!q || !q->x || !q->w || !q->rope || !q->gamma_q || !q->gamma_k) {
+    if (!q || !q->x || !q->w) {
         return fu::fail(FU_E_ARG, "fu_qkv_rope_scatter: null operand");
+    }
+    const int n_types  = q->n_types > 0 ? q->n_types : 3;
+    const int n_normed = q->n_types > 0 ? q->n_normed : 2;
+    if (n_types > 3 || n_normed > 2 || n_normed > n_types) {
+        return fu::fail(FU_E_ARG, "fu_qkv_rope_scatter: %d projections, %d normed", n_types, n_normed);
+    }
+    if (n_normed > 0 && (!q->rope || !q->gamma_q || (n_normed > 1 && !q->gamma_k))) {
+        return fu::fail(FU_E_ARG, "fu_qkv_rope_scatter: RMSNorm + RoPE need rope and gamma tables");
     }
     if (q->world < 1 || q->world > FU_MAX_WORLD || q->rank < 0 || q->rank >= q->world) {
         return fu::fail(FU_E_ARG, "fu_qkv_rope_scatter: rank %d / world %d", q->rank, q->world);
     }
-    if (q->heads < 1 || q->heads > MAX_HEADS || (3 * q->heads) % 2) {
-        return fu::fail(FU_E_ARG, "fu_qkv_rope_scatter: heads=%d (need an even 3*heads <= %d)", q->heads, 3 * MAX_HEADS);
+    if (q->heads < 1 || q->heads > MAX_HEADS) {
+        return fu::fail(FU_E_ARG, "fu_qkv_rope_scatter: heads=%d (need 1..%d)", q->heads, MAX_HEADS);
     }
     if (q->s_local <= 0 || q->m % q->s_local) {
         return fu::fail(FU_E_ARG, "fu_qkv_rope_scatter: m=%lld is not a multiple of s_local=%lld", (long long)q->m,
                         (long long)q->s_local);
     }
     QkvArgs a{};
-    int     rc = fill_core(a.core, q->x, q->w, q->m, 3LL * q->heads * HEAD_DIM, q->k, q->ldx, q->ldw, q->err);
+    int     rc = fill_core(a.core, q->x, q->w, q->m, static_cast<int64_t>(n_types) * q->heads * HEAD_DIM, q->k, q->ldx, q->ldw,
+                           q->err);
     if (rc != FU_OK) {
         return rc;
     }
@@ -542,7 +566,7 @@ extern "C" int fu_qkv_rope_scatter(const FuQkvArgs* q, void* stream)
             e.owner[h] = static_cast<uint8_t>(p);
             e.local[h] = static_cast<uint8_t>(i);
         }
-        if (!q->win_q[p] || !q->win_k[p] || !q->win_v[p] || !q->peer_ctrl[p]) {
+        if (!q->win_q[p] || (n_types > 1 && !q->win_k[p]) || (n_types > 2 && !q->win_v[p]) || !q->peer_ctrl[p]) {
             return fu::fail(FU_E_ARG, "fu_qkv_rope_scatter: no window for rank %d", p);
         }
         e.win[0][p]     = static_cast<uint8_t*>(q->win_q[p]);
@@ -568,6 +592,13 @@ extern "C" int fu_qkv_rope_scatter(const FuQkvArgs* q, void* stream)
     e.s_local          = q->s_local;
     e.seq_off          = q->seq_off;
     e.s_total          = q->s_total;
+    e.n_types          = n_types;
+    e.n_normed         = n_normed;
+    e.y_save           = static_cast<__nv_bfloat16*>(q->y_save);
+    e.ld_y             = q->ld_y;
+    if (q->y_save && ((q->ld_y % 8) || (reinterpret_cast<uintptr_t>(q->y_save) & 15u))) {
+        return fu::fail(FU_E_ARG, "fu_qkv_rope_scatter: y_save needs 16-byte aligned rows");
+    }
     rc                 = set_smem(qkv_rope_scatter_kernel);
     if (rc != FU_OK) {
         return rc;

@@ -484,6 +484,8 @@ TORCH_LIBRARY(fast_ulysses_b200, m)
         .def("set_timeout_ms", &fu::Group::set_timeout_ms)
         .def("set_ctas", &fu::Group::set_ctas)
         .def("windows_allocated", &fu::Group::windows_allocated)
+        .def("symm_alloc", &fu::Group::symm_alloc)
+        .def("symm_ptrs", &fu::Group::symm_ptrs)
         .def("barrier",
              [](const c10::intrusive_ptr<fu::Group>& self, int64_t role) {
                  const c10::cuda::CUDAGuard guard(static_cast<c10::DeviceIndex>(self->device_index()));

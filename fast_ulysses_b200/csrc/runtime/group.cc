@@ -282,6 +282,31 @@ at::Tensor Group::make_output(at::IntArrayRef shape, at::ScalarType dtype, int64
     return out;
 }
 
+at::Tensor Group::symm_alloc(int64_t bytes)
+{
+    check_alive();
+    TORCH_CHECK(on_cuda(), "symmetric buffers exist only on the CUDA backend");
+    prune_owned();
+    Window     w   = allocate(bytes);
+    at::Tensor out = w.bytes.narrow(0, 0, bytes);
+    owned_.emplace(w.bytes.data_ptr(), std::move(w));
+    return out;
+}
+
+std::vector<int64_t> Group::symm_ptrs(const at::Tensor& t) const
+{
+    const Window* w = window_of(t);
+    TORCH_CHECK(w, "this tensor is not the base of a symmetric buffer of this group");
+    std::vector<int64_t> out;
+    for (uint8_t* p : w->base) {
+        out.push_back(reinterpret_cast<int64_t>(p));
+    }
+    for (FuCtrl* p : w->ctrl) {
+        out.push_back(reinterpret_cast<int64_t>(p));
+    }
+    return out;
+}
+
 const Window* Group::window_of(const at::Tensor& t) const
 {
     auto it = owned_.find(t.data_ptr());

@@ -63,6 +63,11 @@ public:
     Window&       lend_window(int64_t bytes);
     at::Tensor    make_output(at::IntArrayRef shape, at::ScalarType dtype, int64_t window_bytes);
     const Window* window_of(const at::Tensor& t) const;
+    // A caller-owned symmetric byte buffer for the fused operators (q/k/v windows, attention
+    // output): COLLECTIVE. `symm_ptrs` gives its base address on every rank followed by its control
+    // block address on every rank.
+    at::Tensor           symm_alloc(int64_t bytes);
+    std::vector<int64_t> symm_ptrs(const at::Tensor& t) const;
     void          prune_owned();
 
     // Typed view of a window's dense prefix.

@@ -52,7 +52,8 @@ def lib() -> C.CDLL:
         _lib.fu_build_info.restype = C.c_char_p
         _lib.fu_a2a4d.argtypes = [C.POINTER(FuA2AArgs), C.c_void_p]
         _lib.fu_a2a4d.restype = C.c_int
-        for name in ("fu_gemm_bf16", "fu_qkv_rope_scatter", "fu_fmha_fwd", "fu_fmha_bwd", "fu_pull_outproj"):
+        for name in ("fu_gemm_bf16", "fu_qkv_rope_scatter", "fu_fmha_fwd", "fu_fmha_bwd", "fu_pull_outproj",
+                     "fu_qk_norm_rope_bwd"):
             getattr(_lib, name).restype = C.c_int
             getattr(_lib, name).argtypes = [C.c_void_p, C.c_void_p]
     return _lib
@@ -83,7 +84,8 @@ class FuQkvArgs(C.Structure):
                 ("head_splits", C.c_int32 * FU_MAX_WORLD), ("win_q", C.c_void_p * FU_MAX_WORLD),
                 ("win_k", C.c_void_p * FU_MAX_WORLD), ("win_v", C.c_void_p * FU_MAX_WORLD),
                 ("peer_ctrl", C.c_void_p * FU_MAX_WORLD), ("flags", C.c_int32), ("timeout_ms", C.c_uint32),
-                ("ctas", C.c_int32), ("err", C.c_void_p)]
+                ("ctas", C.c_int32), ("err", C.c_void_p), ("n_types", C.c_int32), ("n_normed", C.c_int32),
+                ("y_save", C.c_void_p), ("ld_y", C.c_int64)]
 
 
 def stream_ptr():
@@ -113,3 +115,10 @@ class FuPullArgs(C.Structure):
                 ("peer_ctrl", C.c_void_p * FU_MAX_WORLD), ("gather", C.c_void_p), ("ready", C.c_void_p),
                 ("flags", C.c_int32), ("timeout_ms", C.c_uint32), ("ctas", C.c_int32), ("pad_", C.c_int32),
                 ("err", C.c_void_p)]
+
+
+class FuNormRopeBwdArgs(C.Structure):
+    _fields_ = [("dq", C.c_void_p), ("dk", C.c_void_p), ("y", C.c_void_p), ("dy", C.c_void_p), ("rope", C.c_void_p),
+                ("gamma_q", C.c_void_p), ("gamma_k", C.c_void_p), ("dgamma_q", C.c_void_p), ("dgamma_k", C.c_void_p),
+                ("m", C.c_int64), ("s_local", C.c_int64), ("ld_y", C.c_int64), ("ld_dy", C.c_int64),
+                ("heads", C.c_int32), ("eps", C.c_float)]

@@ -57,16 +57,20 @@ def attention_reference(q, k, v, scale=None):
     return o, lse
 
 
-def fmha_bwd(q, k, v, o, lse, d_o, *, scale: float | None = None, ctas: int = 0):
+def fmha_bwd(q, k, v, o, lse, d_o, *, scale: float | None = None, ctas: int = 0, out=None):
     """Gradients of ``fmha_fwd``. All tensors (b, s, h, 128) bf16; ``d_o`` must share ``o``'s
     strides. Returns ``(dq, dk, dv)`` shaped and strided like q, k, v (dense)."""
     b, sq, h, d = q.shape
     if d_o.stride() != o.stride():
         d_o = d_o.contiguous()
         o = o.contiguous()
-    dq = torch.empty(b, sq, h, d, dtype=torch.bfloat16, device=q.device)
-    dk = torch.empty(b, k.shape[1], h, d, dtype=torch.bfloat16, device=q.device)
-    dv = torch.empty_like(dk)
+    if out is not None:
+        dq, dk, dv = out  # dense (b, s, h, 128) tensors provided by the caller
+        assert dq.is_contiguous() and dk.is_contiguous() and dv.is_contiguous()
+    else:
+        dq = torch.empty(b, sq, h, d, dtype=torch.bfloat16, device=q.device)
+        dk = torch.empty(b, k.shape[1], h, d, dtype=torch.bfloat16, device=q.device)
+        dv = torch.empty_like(dk)
     # the launcher addresses dq/dk/dv with the strides of q/k/v: hand it dense q/k/v views
     qc, kc, vc = (t if t.is_contiguous() else t.contiguous() for t in (q, k, v))
     sq_pad = (sq + 127) // 128 * 128

@@ -65,3 +65,21 @@ def qkv_reference(x: torch.Tensor, w: torch.Tensor, rope: torch.Tensor, gamma_q:
         return apply_rope_reference(t, rope).reshape(-1, heads, HEAD_DIM)
 
     return rot(norm(q, gamma_q)), rot(norm(k, gamma_k)), v
+
+
+def qk_norm_rope_bwd(dq, dk, y_save, dy, rope, gamma_q, gamma_k, dgamma_q, dgamma_k, *, heads: int, s_local: int,
+                     eps: float = 1e-6) -> None:
+    """Backward of per-head RMSNorm -> RoPE for q and k (csrc/kernels/elementwise.cu). ``dq``/``dk``:
+    (m, heads*128) bf16 dense; ``y_save``: (m, 2*heads*128) pre-norm projections; ``dy`` receives
+    the q part at column 0 and the k part at column heads*128; ``dgamma_*`` fp32[128] accumulate."""
+    m = dq.shape[0]
+    assert dq.is_contiguous() and dk.is_contiguous() and dq.dtype == torch.bfloat16
+    assert y_save.stride(1) == 1 and dy.stride(1) == 1
+    a = ck.FuNormRopeBwdArgs()
+    a.dq, a.dk, a.y, a.dy = dq.data_ptr(), dk.data_ptr(), y_save.data_ptr(), dy.data_ptr()
+    gq, gk = gamma_q.detach().float().contiguous(), gamma_k.detach().float().contiguous()
+    a.rope, a.gamma_q, a.gamma_k = rope.data_ptr(), gq.data_ptr(), gk.data_ptr()
+    a.dgamma_q, a.dgamma_k = dgamma_q.data_ptr(), dgamma_k.data_ptr()
+    a.m, a.s_local, a.ld_y, a.ld_dy = m, s_local, y_save.stride(0), dy.stride(0)
+    a.heads, a.eps = heads, eps
+    ck.check(ck.lib().fu_qk_norm_rope_bwd(C.byref(a), ck.stream_ptr()))

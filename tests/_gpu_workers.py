@@ -352,3 +352,84 @@ def peer_timeout_is_reported(rank, world):
     assert torch.ones(8, device=dev).sum().item() == 8  # context alive
     dist.barrier()
     g.destroy()
+
+
+def sp_attention_block(rank, world):
+    """The fused sequence-parallel attention block (scatter epilogue, attention, pull prologue)
+    against the same block without sequence parallelism on the full sequence; uneven shards."""
+    from fast_ulysses_b200.models.attention import UlyssesSelfAttention, reference_attention
+    from fast_ulysses_b200.ops import gemm
+
+    dev = torch.device("cuda", rank)
+    g = UlyssesGroup(device=dev)
+    grid, hidden, heads = (4, 10, 16), 768, 6  # 640 tokens
+    total = grid[0] * grid[1] * grid[2]
+    base = total // world
+    seq = [base + (8 if p == 0 else 0) - (8 if p == world - 1 else 0) for p in range(world)] if world > 1 else [total]
+    hs = [heads // world + (1 if p < heads % world else 0) for p in range(world)]
+    torch.manual_seed(42)  # identical weights on every rank
+    attn = UlyssesSelfAttention(g, hidden, heads, grid=grid, seq_splits=seq, head_splits=hs)
+    with torch.no_grad():
+        attn.gamma_q.add_(0.1 * torch.randn_like(attn.gamma_q))
+        attn.gamma_k.add_(0.1 * torch.randn_like(attn.gamma_k))
+    x_full = torch.randn(1, total, hidden, device=dev).bfloat16()
+    dy_full = torch.randn(1, total, hidden, device=dev).bfloat16()
+    s0 = sum(seq[:rank])
+    x = x_full[:, s0:s0 + seq[rank]].clone().requires_grad_()
+    for _ in range(2):  # twice: the windows are reused, the handshakes must keep them apart
+        if x.grad is not None:
+            x.grad = None
+            attn.zero_grad()
+        y = attn(x)
+        y.backward(dy_full[:, s0:s0 + seq[rank]])
+    gemm.check_errors()
+    g.check()
+
+    params = [attn.w_qkv, attn.gamma_q, attn.gamma_k, attn.w_o, attn.b_o]
+    xr = x_full.float().requires_grad_()
+    pr = [p.detach().float().requires_grad_() for p in params]
+    yr = reference_attention(xr, *pr, heads, grid)
+    yr.backward(dy_full.float())
+
+    def rel(a, b):
+        return ((a.float() - b.float()).norm() / b.float().norm().clamp_min(1e-12)).item()
+
+    assert rel(y, yr[:, s0:s0 + seq[rank]]) < 2e-2, ("y", rel(y, yr[:, s0:s0 + seq[rank]]))
+    assert rel(x.grad, xr.grad[:, s0:s0 + seq[rank]]) < 3e-2, ("dx", rel(x.grad, xr.grad[:, s0:s0 + seq[rank]]))
+    for name, p, r in zip(("w_qkv", "gamma_q", "gamma_k", "w_o", "b_o"), params, pr):
+        gsum = p.grad.float().clone()
+        dist.all_reduce(gsum)
+        assert rel(gsum, r.grad) < 4e-2, (name, rel(gsum, r.grad))
+    g.destroy()
+
+
+def dit_stack(rank, world):
+    from fast_ulysses_b200.models.dit import DiTStack, reference_forward
+    from fast_ulysses_b200.ops import gemm
+
+    dev = torch.device("cuda", rank)
+    g = UlyssesGroup(device=dev)
+    grid = (2, 8, 16 * world)
+    total = grid[0] * grid[1] * grid[2]
+    torch.manual_seed(7)
+    stack = DiTStack(g, depth=2, hidden=256 * max(1, world // 2), heads=2 * max(1, world // 2), ffn=512, grid=grid)
+    hidden = stack.blocks[0].hidden
+    x_full = torch.randn(1, total, hidden, device=dev).bfloat16()
+    s_local = total // world
+    x = x_full[:, rank * s_local:(rank + 1) * s_local].clone().requires_grad_()
+    y = stack(x)
+    y.float().pow(2).sum().backward()
+    stack.allreduce_grads()
+    gemm.check_errors()
+    g.check()
+    xr = x_full.float().requires_grad_()
+    yr = reference_forward(stack, xr)
+    yr.pow(2).sum().backward()
+
+    def rel(a, b):
+        return ((a.float() - b.float()).norm() / b.float().norm().clamp_min(1e-12)).item()
+
+    sl = slice(rank * s_local, (rank + 1) * s_local)
+    assert rel(y, yr[:, sl]) < 3e-2, rel(y, yr[:, sl])
+    assert rel(x.grad, xr.grad[:, sl]) < 8e-2, rel(x.grad, xr.grad[:, sl])
+    g.destroy()

@@ -70,3 +70,15 @@ def test_subgroups():
 @pytest.mark.parametrize("world", world_sizes()[:1])
 def test_peer_timeout_is_reported(world):
     run_ranks(world, "_gpu_workers", "peer_timeout_is_reported", backend="nccl", timeout=300)
+
+
+@pytest.mark.parametrize("world", world_sizes())
+def test_sp_attention_block(world):
+    run_ranks(world, "_gpu_workers", "sp_attention_block", backend="nccl", timeout=300)
+
+
+@pytest.mark.parametrize("world", world_sizes()[:1])
+def test_dit_stack(world):
+    if world not in (2, 4, 8):
+        pytest.skip("even world sizes")
+    run_ranks(world, "_gpu_workers", "dit_stack", backend="nccl", timeout=300)
