@@ -218,6 +218,12 @@ FU_API int fu_fmha_fwd(const FuFmhaArgs* args, void* stream);
 // d_o is addressed with o's strides, dq / dk / dv with q's / k's / v's strides.
 FU_API int fu_fmha_bwd(const FuFmhaArgs* args, void* stream);
 
+
+// ---- block-scaled fp8 payloads ----------------------------------------------------------------------
+// `blocks` runs of 128 bf16 values <-> `blocks` packed rows of 144 bytes (128 e4m3 + fp32 scale + pad).
+FU_API int fu_quant_e4m3_block128(const void* x_bf16, void* packed, int64_t blocks, void* stream);
+FU_API int fu_dequant_e4m3_block128(const void* packed, void* x_bf16, int64_t blocks, void* stream);
+
 FU_API const char* fu_last_error(void);
 FU_API const char* fu_build_info(void);  // "sm_100a;<nvcc version>;<library version>"
 

@@ -199,3 +199,26 @@ def fake_tensor(rank, world):
         y = torch.ops.fast_ulysses_b200.all_to_all_4d(g._handle, x, 0, None, None)
         assert tuple(y.shape) == (2, 5 * world, 3, 8)
     g.destroy()
+
+
+def fp8_exchange(rank, world):
+    """Uneven heads [14, 13, 13]-style and +-10% sequence shards: the packed fp8 tensor goes through
+    the same exchange, scales included, and matches the fp32 permutation up to fp8 rounding."""
+    from fast_ulysses_b200.ops import fp8
+
+    g = UlyssesGroup(device="cpu")
+    heads = [5, 4, 4][:world]
+    gen = torch.Generator().manual_seed(99)
+    seq = [int(40 * (0.9 + 0.2 * torch.rand(1, generator=gen).item())) for _ in range(world)]
+    torch.manual_seed(5 + rank)
+    x = (torch.randn(1, seq[rank], sum(heads), 128) * 3).bfloat16()
+    y = fp8.all_to_all_4d_fp8(g, x, mode=0, seq_splits=seq, head_splits=heads)
+    want = reference_uneven(x.float(), 0, seq, heads, rank, world)
+    assert y.shape == want.shape
+    amax = want.abs().amax(-1, keepdim=True).clamp_min(1e-30)
+    assert ((y.float() - want).abs() / amax).max() < 0.07
+    # int8 payloads travel as bytes
+    xi = torch.randint(-100, 100, (1, seq[rank], sum(heads), 128), dtype=torch.int8)
+    yi = g.all_to_all_4d(xi, mode=0, seq_splits=seq, head_splits=heads)
+    assert torch.equal(yi, reference_uneven(xi, 0, seq, heads, rank, world))
+    g.destroy()
