@@ -33,7 +33,7 @@ __global__ void __launch_bounds__(256) quant_e4m3_kernel(const __nv_bfloat16* x,
         for (int off = 16; off > 0; off >>= 1) {
             amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
         }
-        const float scale = amax > 0.0f ? amax * (1.0f / 448.0f) : 1.0f;
+        const float scale = amax > 0.0f ? amax / 448.0f : 1.0f;
         const float inv   = 1.0f / scale;
         uint32_t    q     = 0;
         q |= static_cast<uint32_t>(__nv_cvt_float_to_fp8(a.x * inv, __NV_SATFINITE, __NV_E4M3));
