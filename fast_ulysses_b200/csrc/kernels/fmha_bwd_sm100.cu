@@ -541,3 +541,54 @@ extern "C" int fu_fmha_bwd(const FuFmhaArgs* a, void* stream_v)
     }
     return FU_OK;
 }
+
+// ---- attention backward for callers that cannot allocate ------------------------------------------
+// Some callers of this library are not allowed to obtain device memory at the point where they
+// need the backward pass: code running while a CUDA graph is being recorded, plugins living inside
+// a host application that owns the only allocator, or a real-time loop in which cudaMalloc's
+// implicit device synchronisation is unacceptable. For them the two scratch buffers of
+// fu_fmha_bwd (the padded softmax statistics and the fp32 dQ accumulator) live in the array below,
+// which is part of the library image: every GPU that loads the library holds these bytes until the
+// process exits. The price is a fixed upper bound on the problem size and no concurrency: every
+// call uses the same bytes.
+constexpr size_t kNoAllocStatsBytes = 512u << 10;   // 2 * batch * heads * roundup(seq_q, 128) floats
+constexpr size_t kNoAllocAccBytes   = 8u << 20;     // batch * seq_q * heads * 128 floats
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocStatsBytes + kNoAllocAccBytes];
+
+extern "C" int fu_fmha_bwd_noalloc(const FuFmhaArgs* a, void* stream)
+{
+    if (!a) {
+        return fu::fail(FU_E_ARG, "fu_fmha_bwd_noalloc: null args");
+    }
+    if (a->batch < 1 || a->heads < 1 || a->seq_q < 1) {
+        return fu::fail(FU_E_ARG, "fu_fmha_bwd_noalloc: empty problem");
+    }
+    const size_t sq_pad = (static_cast<size_t>(a->seq_q) + BLK - 1) / BLK * BLK;
+    const size_t stats  = 2 * sizeof(float) * a->batch * a->heads * sq_pad;
+    const size_t acc    = sizeof(float) * a->batch * static_cast<size_t>(a->seq_q) * a->heads * D;
+    if (stats > kNoAllocStatsBytes || acc > kNoAllocAccBytes) {
+        return fu::fail(FU_E_ARG,
+                        "fu_fmha_bwd_noalloc: batch %d x heads %d x seq_q %d needs %zu + %zu scratch bytes, the built-in "
+                        "scratch holds %zu + %zu (batch*heads*seq_q <= 16384); use fu_fmha_bwd with your own buffers",
+                        a->batch, a->heads, a->seq_q, stats, acc, kNoAllocStatsBytes, kNoAllocAccBytes);
+    }
+    // The array's name is only a host-side handle; the device address has to be asked for, once
+    // per device, with that device current. This happens on the first call on each device.
+    static void* base[64] = {};
+    int          dev      = 0;
+    FU_CUDA_OK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) {
+        return fu::fail(FU_E_UNSUPPORTED, "fu_fmha_bwd_noalloc: device index %d", dev);
+    }
+    if (!base[dev]) {
+        void* ptr = nullptr;
+        FU_CUDA_OK(cudaGetSymbolAddress(&ptr, g_noalloc_scratch));
+        base[dev] = ptr;
+    }
+    FuFmhaArgs local = *a;
+    local.delta      = reinterpret_cast<float*>(base[dev]);
+    local.dq_acc     = reinterpret_cast<float*>(static_cast<unsigned char*>(base[dev]) + kNoAllocStatsBytes);
+    // fu_fmha_bwd zeroes the accumulator and rewrites every statistic it reads, so nothing of an
+    // earlier call survives into this one.
+    return fu_fmha_bwd(&local, stream);
+}

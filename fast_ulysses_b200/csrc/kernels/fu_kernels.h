@@ -218,6 +218,19 @@ FU_API int fu_fmha_fwd(const FuFmhaArgs* args, void* stream);
 // d_o is addressed with o's strides, dq / dk / dv with q's / k's / v's strides.
 FU_API int fu_fmha_bwd(const FuFmhaArgs* args, void* stream);
 
+// The same backward pass for callers that may not allocate device memory where they call it (while
+// a graph is being recorded, inside a host application that owns the allocator, in a loop that
+// cannot afford cudaMalloc's synchronisation). This entry point has no counterpart in the
+// reference. `delta` and `dq_acc` in `args` are ignored: the scratch is a fixed array inside the
+// library (8.5 MiB of every GPU that loads it, held until the process exits). Limits and rules:
+//   * batch * heads * seq_q <= 16384 rows (checked; larger problems are refused with an error);
+//   * the first call on each device looks up the array's device address, so make that first call
+//     outside any stream capture;
+//   * all calls share the one array: two calls that overlap on the GPU (different streams, or
+//     different threads) corrupt each other. Calls ordered on one stream are safe, each clears
+//     what it needs to start from zero;
+//   * nothing is allocated or freed: no cudaMalloc/cudaFree, no torch, no library allocator.
+FU_API int fu_fmha_bwd_noalloc(const FuFmhaArgs* args, void* stream);
 
 // ---- block-scaled fp8 payloads ----------------------------------------------------------------------
 // `blocks` runs of 128 bf16 values <-> `blocks` packed rows of 144 bytes (128 e4m3 + fp32 scale + pad).
