@@ -362,7 +362,7 @@ def sp_attention_block(rank, world):
 
     dev = torch.device("cuda", rank)
     g = UlyssesGroup(device=dev)
-    grid, hidden, heads = (4, 10, 16), 768, 6  # 640 tokens
+    grid, hidden, heads = (4, 10, 16), 768, (6 if world <= 6 else 8)  # 640 tokens
     total = grid[0] * grid[1] * grid[2]
     base = total // world
     seq = [base + (8 if p == 0 else 0) - (8 if p == world - 1 else 0) for p in range(world)] if world > 1 else [total]
