@@ -79,6 +79,9 @@ __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float 
     asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
 
+// kDq = true: the single-pass variant that also produces dQ (atomic reductions into dq_acc).
+// kDq = false (default path): dK and dV only; dQ comes from the dQ pass in fmha_bwd_dq_sm100.cu.
+template <bool kDq>
 __global__ void __launch_bounds__(THREADS, 1) fmha_bwd_kernel(const __grid_constant__ Params p)
 {
     extern __shared__ __align__(1024) uint8_t sm[];
@@ -184,7 +187,7 @@ __global__ void __launch_bounds__(THREADS, 1) fmha_bwd_kernel(const __grid_const
                     const uint32_t qa = base + OFF_STAGE + s * STAGE_BYTES;
                     const uint32_t oa = qa + TILE_BYTES;
                     if (!ptx::mbar_wait(&bar.full[s], (it / STAGES) & 1u)
-                        || !ptx::mbar_wait(&bar.st_free, (it & 1u) ^ 1u)) {
+                        || (kDq && !ptx::mbar_wait(&bar.st_free, (it & 1u) ^ 1u))) {
                         flag(p, ERR_MMA);
                         ok = false;
                         break;
@@ -222,13 +225,17 @@ __global__ void __launch_bounds__(THREADS, 1) fmha_bwd_kernel(const __grid_const
                                         ptx::smem_desc_sw128(qa + kk * 2048, HALF_BYTES, 1024), idesc_tn,
                                         i != 0 || kk != 0);
                     }
+                    if (kDq) {
 #pragma unroll
-                    for (int kk = 0; kk < BLK / 16; ++kk) {  // dQ_i = dS K      (contraction over kv)
-                        ptx::mma_f16_ss(tmem, ptx::smem_desc_sw128(dsa + kk * 2048, HALF_BYTES, 1024),
-                                        ptx::smem_desc_sw128(ka + kk * 2048, HALF_BYTES, 1024), idesc_nn, kk != 0);
+                        for (int kk = 0; kk < BLK / 16; ++kk) {  // dQ_i = dS K      (contraction over kv)
+                            ptx::mma_f16_ss(tmem, ptx::smem_desc_sw128(dsa + kk * 2048, HALF_BYTES, 1024),
+                                            ptx::smem_desc_sw128(ka + kk * 2048, HALF_BYTES, 1024), idesc_nn, kk != 0);
+                        }
                     }
                     ptx::mma_commit(&bar.empty[s]);
-                    ptx::mma_commit(&bar.dq_full);
+                    if (kDq) {
+                        ptx::mma_commit(&bar.dq_full);
+                    }
                 }
                 if (ok) {
                     ptx::mma_commit(&bar.acc_full);
@@ -291,7 +298,7 @@ __global__ void __launch_bounds__(THREADS, 1) fmha_bwd_kernel(const __grid_const
                     // dS^T row into the 128B-swizzled [kv x q] tile the dQ MMA reads from shared memory
                     uint8_t* half_base = ds_row + (ch >> 1) * HALF_BYTES;
 #pragma unroll
-                    for (int k4 = 0; k4 < 4; ++k4) {
+                    for (int k4 = 0; kDq && k4 < 4; ++k4) {
                         const int chunk = (ch & 1) * 4 + k4;
                         *reinterpret_cast<uint4*>(half_base + ((chunk ^ (row_in & 7)) << 4)) =
                             make_uint4(dd[4 * k4], dd[4 * k4 + 1], dd[4 * k4 + 2], dd[4 * k4 + 3]);
@@ -301,6 +308,9 @@ __global__ void __launch_bounds__(THREADS, 1) fmha_bwd_kernel(const __grid_const
                 ptx::fence_proxy_async_smem();
                 ptx::tc_fence_before();
                 ptx::mbar_arrive(&bar.p_ready);
+                if (!kDq) {
+                    continue;
+                }
 
                 // dQ_i: this thread now owns query row i * 128 + row_in
                 if (!ptx::mbar_wait(&bar.dq_full, it & 1u)) {
@@ -447,10 +457,12 @@ __global__ void fmha_bwd_post_kernel(const float* acc, __nv_bfloat16* dq, int64_
 
 }  // namespace
 
+int fu_fmha_bwd_dq_launch(const FuFmhaArgs* a, const float* lse2, const float* delta, int sq_pad, void* stream);
+
 extern "C" int fu_fmha_bwd(const FuFmhaArgs* a, void* stream_v)
 {
     if (!a || !a->q || !a->k || !a->v || !a->o || !a->lse || !a->d_o || !a->dq || !a->dk || !a->dv || !a->delta
-        || !a->dq_acc) {
+        || ((a->pad_ & 1) && !a->dq_acc)) {
         return fu::fail(FU_E_ARG, "fu_fmha_bwd: null operand");
     }
     if (a->head_dim != D) {
@@ -481,8 +493,11 @@ extern "C" int fu_fmha_bwd(const FuFmhaArgs* a, void* stream_v)
         fmha_bwd_pre_kernel<<<static_cast<unsigned>((threads + 255) / 256), 256, 0, stream>>>(pre);
         FU_CUDA_OK(cudaGetLastError());
     }
-    FU_CUDA_OK(cudaMemsetAsync(a->dq_acc, 0, sizeof(float) * a->batch * static_cast<int64_t>(a->seq_q) * a->heads * D,
-                               stream));
+    const bool single_pass = (a->pad_ & 1) != 0;
+    if (single_pass) {
+        FU_CUDA_OK(cudaMemsetAsync(a->dq_acc, 0,
+                                   sizeof(float) * a->batch * static_cast<int64_t>(a->seq_q) * a->heads * D, stream));
+    }
 
     Params p{};
     int    rc = make_map_bshd(&p.map_q, a->q, a->batch, a->seq_q, a->heads, a->q_row, a->q_head, a->q_batch, BLK);
@@ -526,12 +541,20 @@ extern "C" int fu_fmha_bwd(const FuFmhaArgs* a, void* stream_v)
     FU_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
     static bool configured[64] = {};
     if (dev < 64 && !configured[dev]) {
-        FU_CUDA_OK(cudaFuncSetAttribute(fmha_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        FU_CUDA_OK(cudaFuncSetAttribute(fmha_bwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        FU_CUDA_OK(cudaFuncSetAttribute(fmha_bwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
         configured[dev] = true;
     }
     int grid = a->ctas > 0 ? std::min(a->ctas, sms) : sms;
     grid     = std::max(1, std::min(grid, p.total_work));
-    fmha_bwd_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(p);
+    if (!single_pass) {
+        // Two passes, no atomics: dK/dV with the K/V block stationary, then dQ with the query rows
+        // stationary (fmha_bwd_dq_sm100.cu). Both read the statistics prepared above.
+        fmha_bwd_kernel<false><<<grid, THREADS, SMEM_BYTES, stream>>>(p);
+        FU_CUDA_OK(cudaGetLastError());
+        return fu_fmha_bwd_dq_launch(a, pre.lse2, pre.delta, sq_pad, stream_v);
+    }
+    fmha_bwd_kernel<true><<<grid, THREADS, SMEM_BYTES, stream>>>(p);
     FU_CUDA_OK(cudaGetLastError());
     {
         const int64_t n = static_cast<int64_t>(a->batch) * a->seq_q * a->heads * 16;

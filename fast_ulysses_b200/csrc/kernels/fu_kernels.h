@@ -204,7 +204,8 @@ typedef struct FuFmhaArgs {
     int64_t     v_row, v_head, v_batch;
     int64_t     o_row, o_head, o_batch;
     int32_t     ctas;
-    int32_t     pad_;
+    int32_t     pad_;    // backward: bit 0 selects the single-pass variant (dQ by atomic reductions
+                         // into dq_acc); 0 = two passes without atomics, dq_acc unused
     uint32_t*   err;
     // backward only
     const void* d_o;

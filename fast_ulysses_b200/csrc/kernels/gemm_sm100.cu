@@ -470,9 +470,8 @@ int fill_core(Core& core, const void* a, const void* b, int64_t m, int64_t n, in
     if (m <= 0 || n <= 0 || k <= 0) {
         return fu::fail(FU_E_ARG, "gemm: empty problem (m=%lld n=%lld k=%lld)", (long long)m, (long long)n, (long long)k);
     }
-    if (k % 8) {
-        return fu::fail(FU_E_ARG, "gemm: k=%lld must be a multiple of 8 (16-byte rows for TMA)", (long long)k);
-    }
+    // K itself may be anything (TMA zero-fills the part of a box that lies past it); what TMA needs
+    // is a 16-byte row pitch, which make_map_2d checks on lda and ldb.
     int rc = make_map_2d(&core.map_a, a, 2, m, k, lda, BM, BK);
     if (rc != FU_OK) {
         return rc;

@@ -57,9 +57,12 @@ def attention_reference(q, k, v, scale=None):
     return o, lse
 
 
-def fmha_bwd(q, k, v, o, lse, d_o, *, scale: float | None = None, ctas: int = 0, out=None):
+def fmha_bwd(q, k, v, o, lse, d_o, *, scale: float | None = None, ctas: int = 0, out=None,
+             single_pass: bool = False):
     """Gradients of ``fmha_fwd``. All tensors (b, s, h, 128) bf16; ``d_o`` must share ``o``'s
-    strides. Returns ``(dq, dk, dv)`` shaped and strided like q, k, v (dense)."""
+    strides. Returns ``(dq, dk, dv)`` shaped and strided like q, k, v (dense). The default runs
+    two passes without atomics (dK/dV with the kv block stationary, dQ with the query rows
+    stationary); ``single_pass=True`` runs the one-kernel variant that reduces dQ atomically."""
     b, sq, h, d = q.shape
     if d_o.stride() != o.stride():
         d_o = d_o.contiguous()
@@ -75,14 +78,17 @@ def fmha_bwd(q, k, v, o, lse, d_o, *, scale: float | None = None, ctas: int = 0,
     qc, kc, vc = (t if t.is_contiguous() else t.contiguous() for t in (q, k, v))
     sq_pad = (sq + 127) // 128 * 128
     stats = torch.empty(2 * b * h * sq_pad, dtype=torch.float32, device=q.device)
-    dq_acc = torch.empty(b, sq, h, d, dtype=torch.float32, device=q.device)
+    dq_acc = torch.empty(b, sq, h, d, dtype=torch.float32, device=q.device) if single_pass else None
     a = ck.FuFmhaArgs()
     _fill(a, qc, kc, vc, o)
     a.lse = lse.data_ptr()
     a.scale = scale if scale is not None else 1.0 / math.sqrt(d)
     a.ctas = ctas
     a.d_o, a.dq, a.dk, a.dv = d_o.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
-    a.delta, a.dq_acc = stats.data_ptr(), dq_acc.data_ptr()
+    a.delta = stats.data_ptr()
+    if single_pass:
+        a.dq_acc = dq_acc.data_ptr()
+        a.pad_ = 1
     ck.check(ck.lib().fu_fmha_bwd(C.byref(a), ck.stream_ptr()))
     return dq, dk, dv
 

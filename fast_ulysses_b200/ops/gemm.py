@@ -34,16 +34,29 @@ def check_errors(device: torch.device | None = None) -> None:
         raise RuntimeError(f"fast_ulysses_b200: a tcgen05 kernel gave up on an internal wait (code {code})")
 
 
+def _tma_ready(x: torch.Tensor) -> torch.Tensor:
+    """A view of ``x`` whose rows are contiguous and start 16 bytes apart (copying if needed)."""
+    if x.stride(1) == 1 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0:
+        return x
+    rows, cols = x.shape
+    buf = torch.empty(rows, (cols + 7) // 8 * 8, dtype=x.dtype, device=x.device)
+    out = buf[:, :cols]
+    out.copy_(x)
+    return out
+
+
+def transpose_for_gemm(x: torch.Tensor) -> torch.Tensor:
+    """``x.t()`` materialised with a 16-byte row pitch, ready to be a K-major GEMM operand."""
+    return _tma_ready(x.t())
+
+
 def gemm_bf16(a: torch.Tensor, b: torch.Tensor, *, bias: torch.Tensor | None = None,
               residual: torch.Tensor | None = None, act: int = 0, out: torch.Tensor | None = None,
               ctas: int = 0) -> torch.Tensor:
     """``out[m, n] = act(a[m, :] . b[n, :] + bias[n]) + residual[m, n]`` (bf16 in, bf16 out)."""
     assert a.is_cuda and b.is_cuda and a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
     assert a.dim() == 2 and b.dim() == 2 and a.shape[1] == b.shape[1], (a.shape, b.shape)
-    if a.stride(1) != 1:
-        a = a.contiguous()
-    if b.stride(1) != 1:
-        b = b.contiguous()
+    a, b = _tma_ready(a), _tma_ready(b)
     m, k = a.shape
     n = b.shape[0]
     if out is None:
@@ -84,10 +97,10 @@ class _Linear(torch.autograd.Function):
         gx = gw = gb = None
         if ctx.needs_input_grad[0]:
             # dX[m, k] = sum_n dY[m, n] W[n, k]  ->  A = dY (m x n), B = W^T (k x n)
-            gx = gemm_bf16(gy2, weight.t().contiguous()).view(ctx.x_shape)
+            gx = gemm_bf16(gy2, transpose_for_gemm(weight)).view(ctx.x_shape)
         if ctx.needs_input_grad[1]:
             # dW[n, k] = sum_m dY[m, n] X[m, k]  ->  A = dY^T (n x m), B = X^T (k x m)
-            gw = gemm_bf16(gy2.t().contiguous(), x2.t().contiguous())
+            gw = gemm_bf16(transpose_for_gemm(gy2), transpose_for_gemm(x2))
         if ctx.has_bias and ctx.needs_input_grad[2]:
             gb = gy2.float().sum(0).to(gy.dtype)
         return gx, gw, gb

@@ -364,8 +364,10 @@ def sp_attention_block(rank, world):
     g = UlyssesGroup(device=dev)
     grid, hidden, heads = (4, 10, 16), 768, (6 if world <= 6 else 8)  # 640 tokens
     total = grid[0] * grid[1] * grid[2]
-    base = total // world
-    seq = [base + (8 if p == 0 else 0) - (8 if p == world - 1 else 0) for p in range(world)] if world > 1 else [total]
+    seq = [total // world + (1 if p < total % world else 0) for p in range(world)]
+    if world > 1:
+        seq[0] += 8   # uneven on purpose (and not a multiple of 8: the wgrad contraction length is odd-sized)
+        seq[-1] -= 8
     hs = [heads // world + (1 if p < heads % world else 0) for p in range(world)]
     torch.manual_seed(42)  # identical weights on every rank
     attn = UlyssesSelfAttention(g, hidden, heads, grid=grid, seq_splits=seq, head_splits=hs)

@@ -80,14 +80,15 @@ def test_backward_matches_fp32_autograd(b, h, sq, skv):
     assert rel_err(v.grad, vr.grad) < 2e-2, ("dv", rel_err(v.grad, vr.grad))
 
 
-def test_backward_many_blocks_per_cta():
+@pytest.mark.parametrize("single_pass", [False, True], ids=["two-pass", "single-pass"])
+def test_backward_many_blocks_per_cta(single_pass):
     torch.manual_seed(1)
     q = torch.randn(1, 640, 3, 128, device="cuda").bfloat16()
     k = torch.randn(1, 900, 3, 128, device="cuda").bfloat16()
     v = torch.randn(1, 900, 3, 128, device="cuda").bfloat16()
     o, lse = attention.fmha_fwd(q, k, v)
     d_o = torch.randn_like(o)
-    dq, dk, dv = attention.fmha_bwd(q, k, v, o, lse, d_o, ctas=2)
+    dq, dk, dv = attention.fmha_bwd(q, k, v, o, lse, d_o, ctas=2, single_pass=single_pass)
     gemm.check_errors()
     qr, kr, vr = (t.float().requires_grad_() for t in (q, k, v))
     o_ref, _ = attention.attention_reference(qr, kr, vr)

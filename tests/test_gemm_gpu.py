@@ -13,7 +13,7 @@ def rel_err(got, want):
 
 
 @pytest.mark.parametrize("m,n,k", [(128, 256, 64), (128, 256, 256), (300, 512, 256), (1000, 384, 320),
-                                   (77, 40, 72), (2048, 1536, 1024)])
+                                   (77, 40, 72), (2048, 1536, 1024), (256, 384, 213), (130, 72, 9)])
 def test_gemm_matches_fp32(m, n, k):
     torch.manual_seed(m + n + k)
     a = torch.randn(m, k, device="cuda").bfloat16()
