@@ -35,7 +35,7 @@ constexpr int KV_BYTES   = BN * D * 2;      // 16 KiB (K or V step tile, two 64-
 constexpr int KV_HALF    = KV_BYTES / 2;
 constexpr int STAGE_BYTES = 2 * KV_BYTES;   // K | V
 constexpr int SMEM_BYTES = 2 * QT * TILE_BYTES + STAGES * STAGE_BYTES + 1024;
-constexpr int THREADS    = 32 * 10;
+constexpr int THREADS    = 32 * 18;         // TMA warp, MMA warp, 2 tiles x 8 element-wise warps
 
 enum : uint32_t { ERR_LOAD = 31, ERR_MMA = 32, ERR_COMPUTE = 33 };
 
@@ -92,9 +92,9 @@ __global__ void __launch_bounds__(THREADS, 1) fmha_bwd_dq_kernel(const __grid_co
         }
         for (int t = 0; t < QT; ++t) {
             ptx::mbar_init(&bar.sd_full[t], 1);
-            ptx::mbar_init(&bar.ds_ready[t], 128);
+            ptx::mbar_init(&bar.ds_ready[t], 256);
             ptx::mbar_init(&bar.dq_final[t], 1);
-            ptx::mbar_init(&bar.dq_free[t], 128);
+            ptx::mbar_init(&bar.dq_free[t], 256);
         }
         ptx::mbar_fence_init();
         ptx::tma_prefetch_desc(&p.map_q);
@@ -188,7 +188,7 @@ __global__ void __launch_bounds__(THREADS, 1) fmha_bwd_dq_kernel(const __grid_co
                 for (int kk = 0; kk < BN / 16; ++kk) {
                     // K step tile as an MN-major operand: 16 kv rows = 2048 bytes further down, the two
                     // 64-wide halves of d are KV_HALF apart, 8-row groups 1024 bytes apart
-                    ptx::mma_f16_ts(tmem + t * 256 + 128, tmem + t * 256 + kk * 8,
+                    ptx::mma_f16_ts(tmem + t * 256 + 128, tmem + t * 256 + (kk >> 1) * 32 + (kk & 1) * 8,
                                     ptx::smem_desc_sw128(ka + kk * 2048, KV_HALF, 1024), idesc_dq, accumulate || kk != 0);
                 }
             };
@@ -250,7 +250,10 @@ __global__ void __launch_bounds__(THREADS, 1) fmha_bwd_dq_kernel(const __grid_co
     }
     else {
         // ---------------------------------------------------------------- dS and the dQ epilogue
-        const int      t        = (warp - 2) >> 2;
+        // two threads per query row: each takes 32 of the 64 kv columns of a step (the element-wise
+        // work is latency-bound, so every scheduler gets two warps per tile)
+        const int      t        = (warp - 2) >> 3;
+        const int      colhalf  = ((warp - 2) >> 2) & 1;
         const int      quarter  = warp & 3;
         const int      row_in   = quarter * 32 + lane;
         const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
@@ -278,31 +281,30 @@ __global__ void __launch_bounds__(THREADS, 1) fmha_bwd_dq_kernel(const __grid_co
                 }
                 ptx::tc_fence_after();
                 const int valid = min(BN, p.Skv - j * BN);
-                uint32_t  rs[BN], rd[BN];
-                ptx::tmem_ld_32x32(ts, *reinterpret_cast<uint32_t(*)[32]>(&rs[0]));
-                ptx::tmem_ld_32x32(ts + 32, *reinterpret_cast<uint32_t(*)[32]>(&rs[32]));
-                ptx::tmem_ld_32x32(tdp, *reinterpret_cast<uint32_t(*)[32]>(&rd[0]));
-                ptx::tmem_ld_32x32(tdp + 32, *reinterpret_cast<uint32_t(*)[32]>(&rd[32]));
+                uint32_t  rs[32], rd[32];
+                ptx::tmem_ld_32x32(ts + colhalf * 32, rs);
+                ptx::tmem_ld_32x32(tdp + colhalf * 32, rd);
                 ptx::tmem_ld_wait();
-#pragma unroll
-                for (int ch = 0; ch < 2; ++ch) {
+                {
                     uint32_t pk[16];
 #pragma unroll
                     for (int i = 0; i < 16; ++i) {
-                        const int   k0 = ch * 32 + 2 * i;
-                        float       p0 = ptx::ex2(fmaf(__uint_as_float(rs[k0]), c, -lse2));
-                        float       p1 = ptx::ex2(fmaf(__uint_as_float(rs[k0 + 1]), c, -lse2));
+                        const int k0 = colhalf * 32 + 2 * i;
+                        float     p0 = ptx::ex2(fmaf(__uint_as_float(rs[2 * i]), c, -lse2));
+                        float     p1 = ptx::ex2(fmaf(__uint_as_float(rs[2 * i + 1]), c, -lse2));
                         if (k0 >= valid) {
                             p0 = 0.0f;
                         }
                         if (k0 + 1 >= valid) {
                             p1 = 0.0f;
                         }
-                        const float d0 = p0 * (__uint_as_float(rd[k0]) - dl) * p.scale;
-                        const float d1 = p1 * (__uint_as_float(rd[k0 + 1]) - dl) * p.scale;
+                        const float d0 = p0 * (__uint_as_float(rd[2 * i]) - dl) * p.scale;
+                        const float d1 = p1 * (__uint_as_float(rd[2 * i + 1]) - dl) * p.scale;
                         pk[i]          = ptx::pack_bf16x2(d0, d1);
                     }
-                    ptx::tmem_st_32x16(ts + ch * 16, pk);
+                    // dS over the start of the columns THIS warp read: kv 0..31 at columns 0..15,
+                    // kv 32..63 at columns 32..47 (the MMA addresses its K-steps accordingly)
+                    ptx::tmem_st_32x16(ts + colhalf * 32, pk);
                 }
                 ptx::tmem_st_wait();
                 ptx::tc_fence_before();
@@ -319,7 +321,7 @@ __global__ void __launch_bounds__(THREADS, 1) fmha_bwd_dq_kernel(const __grid_co
             const bool     row_ok = row < p.Sq;
             __nv_bfloat16* dst    = p.dq + b * p.dq_batch + static_cast<int64_t>(row) * p.dq_row + h * p.dq_head;
 #pragma unroll 1
-            for (int c2 = 0; c2 < 2; ++c2) {
+            for (int c2 = colhalf; c2 < colhalf + 1; ++c2) {
                 uint32_t r[64];
                 ptx::tmem_ld_32x32(tdq + c2 * 64, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
                 ptx::tmem_ld_32x32(tdq + c2 * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));

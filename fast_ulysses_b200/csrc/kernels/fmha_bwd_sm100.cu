@@ -458,6 +458,7 @@ __global__ void fmha_bwd_post_kernel(const float* acc, __nv_bfloat16* dq, int64_
 }  // namespace
 
 int fu_fmha_bwd_dq_launch(const FuFmhaArgs* a, const float* lse2, const float* delta, int sq_pad, void* stream);
+int fu_fmha_bwd_dkdv_launch(const FuFmhaArgs* a, const float* lse2, const float* delta, int sq_pad, void* stream);
 
 extern "C" int fu_fmha_bwd(const FuFmhaArgs* a, void* stream_v)
 {
@@ -550,8 +551,17 @@ extern "C" int fu_fmha_bwd(const FuFmhaArgs* a, void* stream_v)
     if (!single_pass) {
         // Two passes, no atomics: dK/dV with the K/V block stationary, then dQ with the query rows
         // stationary (fmha_bwd_dq_sm100.cu). Both read the statistics prepared above.
-        fmha_bwd_kernel<false><<<grid, THREADS, SMEM_BYTES, stream>>>(p);
-        FU_CUDA_OK(cudaGetLastError());
+        if (a->pad_ & 2) {
+            // the earlier dK/dV pass without double buffering, kept for comparison
+            fmha_bwd_kernel<false><<<grid, THREADS, SMEM_BYTES, stream>>>(p);
+            FU_CUDA_OK(cudaGetLastError());
+        }
+        else {
+            rc = fu_fmha_bwd_dkdv_launch(a, pre.lse2, pre.delta, sq_pad, stream_v);
+            if (rc != FU_OK) {
+                return rc;
+            }
+        }
         return fu_fmha_bwd_dq_launch(a, pre.lse2, pre.delta, sq_pad, stream_v);
     }
     fmha_bwd_kernel<true><<<grid, THREADS, SMEM_BYTES, stream>>>(p);

@@ -58,7 +58,7 @@ def attention_reference(q, k, v, scale=None):
 
 
 def fmha_bwd(q, k, v, o, lse, d_o, *, scale: float | None = None, ctas: int = 0, out=None,
-             single_pass: bool = False):
+             single_pass: bool = False, variant: int = 0):
     """Gradients of ``fmha_fwd``. All tensors (b, s, h, 128) bf16; ``d_o`` must share ``o``'s
     strides. Returns ``(dq, dk, dv)`` shaped and strided like q, k, v (dense). The default runs
     two passes without atomics (dK/dV with the kv block stationary, dQ with the query rows
@@ -89,6 +89,8 @@ def fmha_bwd(q, k, v, o, lse, d_o, *, scale: float | None = None, ctas: int = 0,
     if single_pass:
         a.dq_acc = dq_acc.data_ptr()
         a.pad_ = 1
+    elif variant:
+        a.pad_ = variant
     ck.check(ck.lib().fu_fmha_bwd(C.byref(a), ck.stream_ptr()))
     return dq, dk, dv
 
