@@ -10,7 +10,7 @@
 //   dQ_i = dS K            (dS^T in smem read as an MN-major A, K as an MN-major B); added into an
 //                          fp32 accumulator in global memory with vector reductions
 // Tensor memory: S^T/P^T/dQ | dP^T/dS^T | dV | dK, 128 fp32 columns each.
-// Warps: 0 = TMA producer, 1 = MMA issuer, 2..5 = one thread per kv row (and per q row for dQ).
+// Warps: 0 = TMA producer, 1 = MMA issuer, 2..9 = two threads per kv row (and per q row for dQ).
 //
 // A small pre-pass computes delta = rowsum(O o dO) and rescales the log-sum-exp to base 2, both
 // padded to whole query blocks; a post-pass rounds the fp32 dQ accumulator to bf16.
@@ -41,7 +41,7 @@ constexpr int OFF_DS     = OFF_STAGE + STAGES * STAGE_BYTES;
 constexpr int OFF_STATS  = OFF_DS + TILE_BYTES;           // per stage: lse2[128] | delta[128]
 constexpr int OFF_BARS   = OFF_STATS + STAGES * 1024;
 constexpr int SMEM_BYTES = OFF_BARS + 256;
-constexpr int THREADS    = 192;
+constexpr int THREADS    = 320;   // TMA warp, MMA warp, 8 element-wise warps (two threads per row)
 
 static_assert(SMEM_BYTES <= 232448, "shared memory budget");
 
@@ -105,11 +105,11 @@ __global__ void __launch_bounds__(THREADS, 1) fmha_bwd_kernel(const __grid_const
             ptx::mbar_init(&bar.empty[s], 1);
         }
         ptx::mbar_init(&bar.s_full, 1);
-        ptx::mbar_init(&bar.p_ready, 128);
+        ptx::mbar_init(&bar.p_ready, 256);
         ptx::mbar_init(&bar.dq_full, 1);
-        ptx::mbar_init(&bar.st_free, 128);
+        ptx::mbar_init(&bar.st_free, 256);
         ptx::mbar_init(&bar.acc_full, 1);
-        ptx::mbar_init(&bar.acc_free, 128);
+        ptx::mbar_init(&bar.acc_free, 256);
         ptx::mbar_fence_init();
         ptx::tma_prefetch_desc(&p.map_q);
         ptx::tma_prefetch_desc(&p.map_k);
@@ -215,13 +215,13 @@ __global__ void __launch_bounds__(THREADS, 1) fmha_bwd_kernel(const __grid_const
                     ptx::tc_fence_after();
 #pragma unroll
                     for (int kk = 0; kk < BLK / 16; ++kk) {  // dV += P^T dO   (contraction over q)
-                        ptx::mma_f16_ts(tmem + 256, tmem + kk * 8,
+                        ptx::mma_f16_ts(tmem + 256, tmem + (kk >> 2) * 64 + (kk & 3) * 8,
                                         ptx::smem_desc_sw128(oa + kk * 2048, HALF_BYTES, 1024), idesc_tn,
                                         i != 0 || kk != 0);
                     }
 #pragma unroll
                     for (int kk = 0; kk < BLK / 16; ++kk) {  // dK += dS^T Q
-                        ptx::mma_f16_ts(tmem + 384, tmem + 128 + kk * 8,
+                        ptx::mma_f16_ts(tmem + 384, tmem + 128 + (kk >> 2) * 64 + (kk & 3) * 8,
                                         ptx::smem_desc_sw128(qa + kk * 2048, HALF_BYTES, 1024), idesc_tn,
                                         i != 0 || kk != 0);
                     }
@@ -247,7 +247,10 @@ __global__ void __launch_bounds__(THREADS, 1) fmha_bwd_kernel(const __grid_const
     }
     else {
         // ---------------------------------------------------------------- compute: one thread per row
+        // two threads per row: warps 2..5 take columns 0..63 of a tile, warps 6..9 columns 64..127;
+        // each writes its packed bf16 results over the start of the columns it read itself
         const int      quarter  = warp & 3;
+        const int      c2       = (warp - 2) >> 2;
         const int      row_in   = quarter * 32 + lane;
         const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
         const uint32_t t_s = tmem + lane_off, t_dp = tmem + 128 + lane_off;
@@ -273,7 +276,7 @@ __global__ void __launch_bounds__(THREADS, 1) fmha_bwd_kernel(const __grid_const
                 }
                 ptx::tc_fence_after();
 #pragma unroll 1
-                for (int ch = 0; ch < 4; ++ch) {
+                for (int ch = 2 * c2; ch < 2 * c2 + 2; ++ch) {
                     uint32_t rs[32], rd[32];
                     ptx::tmem_ld_32x32(t_s + ch * 32, rs);
                     ptx::tmem_ld_32x32(t_dp + ch * 32, rd);
@@ -293,8 +296,8 @@ __global__ void __launch_bounds__(THREADS, 1) fmha_bwd_kernel(const __grid_const
                         pp[k]          = ptx::pack_bf16x2(p0, p1);
                         dd[k]          = ptx::pack_bf16x2(d0, d1);
                     }
-                    ptx::tmem_st_32x16(t_s + ch * 16, pp);
-                    ptx::tmem_st_32x16(t_dp + ch * 16, dd);
+                    ptx::tmem_st_32x16(t_s + c2 * 64 + (ch & 1) * 16, pp);
+                    ptx::tmem_st_32x16(t_dp + c2 * 64 + (ch & 1) * 16, dd);
                     // dS^T row into the 128B-swizzled [kv x q] tile the dQ MMA reads from shared memory
                     uint8_t* half_base = ds_row + (ch >> 1) * HALF_BYTES;
 #pragma unroll
@@ -322,7 +325,7 @@ __global__ void __launch_bounds__(THREADS, 1) fmha_bwd_kernel(const __grid_const
                 const int qrow = i * BLK + row_in;
                 float*    dq   = p.dq_acc + ((static_cast<int64_t>(b) * p.Sq + qrow) * p.H + h) * D;
 #pragma unroll 1
-                for (int ch = 0; ch < 4; ++ch) {
+                for (int ch = 2 * c2; ch < 2 * c2 + 2; ++ch) {
                     uint32_t r[32];
                     ptx::tmem_ld_32x32(t_s + ch * 32, r);
                     ptx::tmem_ld_wait();
@@ -349,7 +352,7 @@ __global__ void __launch_bounds__(THREADS, 1) fmha_bwd_kernel(const __grid_const
             __nv_bfloat16* dv = p.dv + b * p.dv_batch + static_cast<int64_t>(kvr) * p.dv_row + h * p.dv_head;
             __nv_bfloat16* dk = p.dk + b * p.dk_batch + static_cast<int64_t>(kvr) * p.dk_row + h * p.dk_head;
 #pragma unroll 1
-            for (int ch = 0; ch < 4; ++ch) {
+            for (int ch = 2 * c2; ch < 2 * c2 + 2; ++ch) {
                 uint32_t rv[32], rk[32];
                 ptx::tmem_ld_32x32(t_dv + ch * 32, rv);
                 ptx::tmem_ld_32x32(t_dk + ch * 32, rk);

@@ -435,3 +435,58 @@ def dit_stack(rank, world):
     assert rel(y, yr[:, sl]) < 3e-2, rel(y, yr[:, sl])
     assert rel(x.grad, xr.grad[:, sl]) < 8e-2, rel(x.grad, xr.grad[:, sl])
     g.destroy()
+
+
+def nvlink_probe_matches_nvml_oracle(rank, world):
+    """nvlink_matrix against an independent pynvml walk over the links, pair by pair; the matrix is
+    identical on every rank; the constructor accepts a fully joined group with require_nvlink=True."""
+    import fast_ulysses_b200 as fu
+
+    dev = torch.device("cuda", rank)
+    devices = list(range(world))
+    ours = fu.nvlink_matrix(devices)
+    assert fu.nvlink_matrix([0, 999]) is None and fu._C.check_nvlink([0, 999]) == ""  # fails open
+    try:
+        import pynvml
+
+        pynvml.nvmlInit()
+    except Exception:
+        print("BLIND: no NVML oracle on this machine")
+        return
+    if ours is None:
+        print("BLIND: the probe could not say")
+        return
+
+    def text(v):
+        return (v.decode() if isinstance(v, bytes) else v).lower()[-12:]
+
+    on_switch, direct, ids = {}, {}, {}
+    for i in devices:
+        pr = torch.cuda.get_device_properties(i)
+        bus = f"{pr.pci_domain_id:08x}:{pr.pci_bus_id:02x}:{pr.pci_device_id:02x}.0"
+        h = pynvml.nvmlDeviceGetHandleByPciBusId(bus.encode())
+        ids[i] = text(pynvml.nvmlDeviceGetPciInfo(h).busId)
+        on_switch[i], direct[i] = False, set()
+        for link in range(32):
+            try:
+                if not pynvml.nvmlDeviceGetNvLinkState(h, link):
+                    continue
+                kind = pynvml.nvmlDeviceGetNvLinkRemoteDeviceType(h, link)
+                if kind == 2:
+                    on_switch[i] = True
+                elif kind == 0:
+                    direct[i].add(text(pynvml.nvmlDeviceGetNvLinkRemotePciInfo(h, link).busId))
+            except pynvml.NVMLError:
+                continue
+    for i in devices:
+        for j in devices:
+            if i != j:
+                want = (on_switch[i] and on_switch[j]) or ids[j] in direct[i]
+                assert ours[(i, j)] == want, (i, j, ours[(i, j)], want)
+    flat = torch.tensor([int(ours[(i, j)]) for i in devices for j in devices if i != j], device=dev)
+    gathered = [torch.zeros_like(flat) for _ in range(world)]
+    dist.all_gather(gathered, flat)
+    assert all(torch.equal(gathered[0], t) for t in gathered), "the matrix differs between ranks"
+    if all(ours.values()):
+        g = fu.UlyssesGroup(device=dev, require_nvlink=True)
+        g.destroy()

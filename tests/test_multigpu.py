@@ -82,3 +82,8 @@ def test_dit_stack(world):
     if world not in (2, 4, 8):
         pytest.skip("even world sizes")
     run_ranks(world, "_gpu_workers", "dit_stack", backend="nccl", timeout=300)
+
+
+@pytest.mark.parametrize("world", world_sizes()[:1])
+def test_nvlink_probe_matches_nvml_oracle(world):
+    run_ranks(world, "_gpu_workers", "nvlink_probe_matches_nvml_oracle", backend="nccl", timeout=200)
