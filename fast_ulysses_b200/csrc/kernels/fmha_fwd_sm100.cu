@@ -5,9 +5,7 @@
 //   warp 0       TMA producer: Q (once per item), then K and V tiles through two-stage rings
 //   warp 1       MMA issuer: S_t = Q_t K^T (operands in shared memory), O_t += P_t V (P read
 //                from tensor memory, V as an MN-major shared-memory operand)
-//   warps 2..9   softmax for query tile 0, warps 10..17 for query tile 1: TWO threads per row
-//                (64 kv columns each; the softmax is latency-bound, so every scheduler gets two
-//                warps per tile; the row maximum is exchanged through shared memory);
+//   warps 2..5   softmax for query tile 0, warps 6..9 for query tile 1: one thread per row;
 //                exp2 with a lazily updated reference maximum, P written back over S in tensor
 //                memory as packed bf16, O rescaled in tensor memory only when the maximum grew by
 //                more than 2^8; final normalisation, bf16 store and log-sum-exp
@@ -39,7 +37,7 @@ constexpr int KV_STAGES = 2;
 constexpr int TILE_BYTES = 128 * D * 2;       // 32 KiB: a 128 x 128 bf16 tile as two 64-column halves
 constexpr int HALF_BYTES = TILE_BYTES / 2;
 constexpr int SMEM_BYTES = (QT + 2 * KV_STAGES) * TILE_BYTES + 1024;
-constexpr int THREADS    = 32 * 18;   // TMA warp, MMA warp, 2 query tiles x 8 softmax warps
+constexpr int THREADS    = 32 * 10;
 constexpr float RESCALE_THRESHOLD = 8.0f;     // in log2 units
 
 enum : uint32_t { ERR_LOAD = 11, ERR_MMA = 12, ERR_SOFTMAX = 13 };
@@ -73,7 +71,6 @@ __global__ void __launch_bounds__(THREADS, 1) fmha_fwd_kernel(const __grid_const
     extern __shared__ uint8_t smem_raw[];
     __shared__ Barriers       bar;
     __shared__ uint32_t       tmem_holder;
-    __shared__ float          xchg[QT][2][BM];   // partner exchange: row maximum per step, row sum at the end
 
     const uint32_t base = (ptx::smem_addr(smem_raw) + 1023u) & ~1023u;
     uint8_t*       sm   = smem_raw + (base - ptx::smem_addr(smem_raw));
@@ -99,9 +96,9 @@ __global__ void __launch_bounds__(THREADS, 1) fmha_fwd_kernel(const __grid_const
         }
         for (int t = 0; t < QT; ++t) {
             ptx::mbar_init(&bar.s_full[t], 1);
-            ptx::mbar_init(&bar.p_ready[t], 256);
+            ptx::mbar_init(&bar.p_ready[t], 128);
             ptx::mbar_init(&bar.o_final[t], 1);
-            ptx::mbar_init(&bar.o_free[t], 256);
+            ptx::mbar_init(&bar.o_free[t], 128);
         }
         ptx::mbar_fence_init();
         ptx::tma_prefetch_desc(&p.map_q);
@@ -192,7 +189,7 @@ __global__ void __launch_bounds__(THREADS, 1) fmha_fwd_kernel(const __grid_const
                 for (int kk = 0; kk < BN / 16; ++kk) {
                     // 16 kv rows = 2048 bytes further down; the two 64-wide halves of d are
                     // HALF_BYTES apart (leading byte offset), 8-row groups 1024 bytes apart
-                    ptx::mma_f16_ts(tmem + 256 + t * 128, tmem + t * 128 + (kk >> 2) * 64 + (kk & 3) * 8,
+                    ptx::mma_f16_ts(tmem + 256 + t * 128, tmem + t * 128 + kk * 8,
                                     ptx::smem_desc_sw128(va + kk * 2048, HALF_BYTES, 1024), idesc_pv,
                                     accumulate || kk != 0);
                 }
@@ -265,40 +262,42 @@ __global__ void __launch_bounds__(THREADS, 1) fmha_fwd_kernel(const __grid_const
     }
     else {
         // ---------------------------------------------------------------- softmax + epilogue
-        const int      t        = (warp - 2) >> 3;         // query tile
-        const int      c2       = ((warp - 2) >> 2) & 1;   // which 64 of the 128 kv columns (and of d)
-        const int      quarter  = warp & 3;                // TMEM lane quarter of this warp
-        const int      row_in   = quarter * 32 + lane;     // row inside the query tile
+        const int      t       = (warp - 2) >> 2;          // query tile
+        const int      quarter = warp & 3;                 // TMEM lane quarter of this warp
+        const int      row_in  = quarter * 32 + lane;      // row inside the query tile
         const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
-        const uint32_t ts       = tmem + t * 128 + c2 * 64 + lane_off;        // my half of S_t; P_t goes over it
-        const uint32_t to       = tmem + 256 + t * 128 + c2 * 64 + lane_off;  // my half of O_t
-        const float    c        = p.scale_log2;
+        const uint32_t ts      = tmem + t * 128 + lane_off;        // S_t / P_t
+        const uint32_t to      = tmem + 256 + t * 128 + lane_off;  // O_t
+        const float    c       = p.scale_log2;
         uint32_t       scount = 0, wc = 0;
         bool           ok = true;
-        auto pair_sync = [&]() { asm volatile("bar.sync %0, 256;" ::"r"(1 + t) : "memory"); };
 
         for (int w = blockIdx.x; w < p.total_work && ok; w += gridDim.x, ++wc) {
             const int qb  = w % p.q_blocks;
             const int h   = (w / p.q_blocks) % p.H;
             const int b   = w / (p.q_blocks * p.H);
             const int row = qb * (QT * BM) + t * BM + row_in;
-            float     m_ref = -INFINITY, l = 0.0f;   // l: sum over MY columns only
+            float     m_ref = -INFINITY, l = 0.0f;
 
             for (int j = 0; j < n_kv; ++j, ++scount) {
                 if (!ptx::mbar_wait(&bar.s_full[t], scount & 1u)) {
                     flag(p, ERR_SOFTMAX);
                     ok = false;
+                    break;
                 }
-                // every thread of the tile takes part in the exchange barrier below, also after an error
                 ptx::tc_fence_after();
-                const int valid = min(BN, p.Skv - j * BN) - c2 * 64;  // my columns of this step that exist
-                uint32_t  r[64];
-                ptx::tmem_ld_32x32(ts, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
-                ptx::tmem_ld_32x32(ts + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
-                ptx::tmem_ld_wait();
-                if (valid < 64) {
+                const int valid = min(BN, p.Skv - j * BN);  // columns of this step that exist
+                // The whole row of S in registers with a single wait: the softmax sits on the
+                // critical path between two MMAs, so its latency matters more than its register use.
+                uint32_t r[BN];
 #pragma unroll
-                    for (int i = 0; i < 64; ++i) {
+                for (int ch = 0; ch < 4; ++ch) {
+                    ptx::tmem_ld_32x32(ts + ch * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[ch * 32]));
+                }
+                ptx::tmem_ld_wait();
+                if (valid < BN) {
+#pragma unroll
+                    for (int i = 0; i < BN; ++i) {
                         if (i >= valid) {
                             r[i] = 0xff800000u;  // -inf: exp2 gives exactly 0
                         }
@@ -306,26 +305,20 @@ __global__ void __launch_bounds__(THREADS, 1) fmha_fwd_kernel(const __grid_const
                 }
                 float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-                for (int i = 0; i < 64; i += 4) {
+                for (int i = 0; i < BN; i += 4) {
 #pragma unroll
                     for (int u = 0; u < 4; ++u) {
                         mx4[u] = fmaxf(mx4[u], __uint_as_float(r[i + u]));
                     }
                 }
-                float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-                xchg[t][c2][row_in] = mx;
-                pair_sync();
-                mx = fmaxf(mx, xchg[t][c2 ^ 1][row_in]);
-                if (!ok) {
-                    break;
-                }
+                const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
                 // lazy reference maximum: rescale only when it grew by more than the threshold
                 const bool grow = (j == 0) || ((mx - m_ref) * c > RESCALE_THRESHOLD);
                 if (__any_sync(0xffffffffu, grow && j != 0)) {
                     const float alpha = (grow && j != 0) ? ptx::ex2((m_ref - mx) * c) : 1.0f;
                     l *= alpha;
 #pragma unroll 1
-                    for (int ch = 0; ch < 2; ++ch) {
+                    for (int ch = 0; ch < 4; ++ch) {
                         uint32_t ro[32];
                         ptx::tmem_ld_32x32(to + ch * 32, ro);
                         ptx::tmem_ld_wait();
@@ -341,10 +334,10 @@ __global__ void __launch_bounds__(THREADS, 1) fmha_fwd_kernel(const __grid_const
                     m_ref = mx;
                 }
                 const float mc = m_ref * c;
-                // P = exp2(S * c - m_ref * c) as packed bf16 over the start of MY columns of S
+                // P = exp2(S * c - m_ref * c), written over S as packed bf16
                 float l4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-                for (int ch = 0; ch < 2; ++ch) {
+                for (int ch = 0; ch < 4; ++ch) {
                     uint32_t pk[16];
 #pragma unroll
                     for (int i = 0; i < 16; ++i) {
@@ -363,24 +356,17 @@ __global__ void __launch_bounds__(THREADS, 1) fmha_fwd_kernel(const __grid_const
             if (!ok) {
                 break;
             }
-            // epilogue: O / l -> bf16 (my 64 columns of d), log-sum-exp
+            // epilogue: O / l -> bf16, log-sum-exp
             if (!ptx::mbar_wait(&bar.o_final[t], wc & 1u)) {
                 flag(p, ERR_SOFTMAX);
-                ok = false;
-            }
-            xchg[t][c2][row_in] = l;
-            pair_sync();
-            l += xchg[t][c2 ^ 1][row_in];
-            pair_sync();  // the slots are rewritten by the next item's first step
-            if (!ok) {
                 break;
             }
             ptx::tc_fence_after();
             const float    inv    = 1.0f / l;
             const bool     row_ok = row < p.Sq;
-            __nv_bfloat16* dst    = p.o + b * p.o_batch + static_cast<int64_t>(row) * p.o_row + h * p.o_head + c2 * 64;
+            __nv_bfloat16* dst    = p.o + b * p.o_batch + static_cast<int64_t>(row) * p.o_row + h * p.o_head;
 #pragma unroll 1
-            for (int ch = 0; ch < 2; ++ch) {
+            for (int ch = 0; ch < 4; ++ch) {
                 uint32_t r[32];
                 ptx::tmem_ld_32x32(to + ch * 32, r);
                 ptx::tmem_ld_wait();
@@ -397,7 +383,7 @@ __global__ void __launch_bounds__(THREADS, 1) fmha_fwd_kernel(const __grid_const
                     }
                 }
             }
-            if (row_ok && p.lse && c2 == 0) {
+            if (row_ok && p.lse) {
                 p.lse[(static_cast<int64_t>(b) * p.H + h) * p.Sq + row] = (m_ref * c + ptx::lg2(l)) * 0.6931471805599453f;
             }
             ptx::tc_fence_before();
