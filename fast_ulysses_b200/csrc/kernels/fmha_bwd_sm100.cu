@@ -433,9 +433,9 @@ __global__ void fmha_bwd_pre_kernel(const PreParams p)
     }
 }
 
-// dq[b,s,h,:] = bf16(dq_acc[b,s,h,:])
+// dq[b,s,h,:] = bf16(dq_acc[b,s,h,:] * scale)
 __global__ void fmha_bwd_post_kernel(const float* acc, __nv_bfloat16* dq, int64_t dq_row, int64_t dq_head,
-                                     int64_t dq_batch, int B, int H, int Sq)
+                                     int64_t dq_batch, int B, int H, int Sq, float scale)
 {
     const int64_t idx   = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;  // one per 8 elements
     const int64_t total = static_cast<int64_t>(B) * Sq * H * 16;
@@ -451,10 +451,10 @@ __global__ void fmha_bwd_post_kernel(const float* acc, __nv_bfloat16* dq, int64_
     const float4  a0 = *reinterpret_cast<const float4*>(acc + r * 128 + x8 * 8);
     const float4  a1 = *reinterpret_cast<const float4*>(acc + r * 128 + x8 * 8 + 4);
     uint4         o;
-    o.x = ptx::pack_bf16x2(a0.x, a0.y);
-    o.y = ptx::pack_bf16x2(a0.z, a0.w);
-    o.z = ptx::pack_bf16x2(a1.x, a1.y);
-    o.w = ptx::pack_bf16x2(a1.z, a1.w);
+    o.x = ptx::pack_bf16x2(a0.x * scale, a0.y * scale);
+    o.y = ptx::pack_bf16x2(a0.z * scale, a0.w * scale);
+    o.z = ptx::pack_bf16x2(a1.x * scale, a1.y * scale);
+    o.w = ptx::pack_bf16x2(a1.z * scale, a1.w * scale);
     *reinterpret_cast<uint4*>(dq + b * dq_batch + static_cast<int64_t>(s) * dq_row + h * dq_head + x8 * 8) = o;
 }
 
@@ -462,11 +462,12 @@ __global__ void fmha_bwd_post_kernel(const float* acc, __nv_bfloat16* dq, int64_
 
 int fu_fmha_bwd_dq_launch(const FuFmhaArgs* a, const float* lse2, const float* delta, int sq_pad, void* stream);
 int fu_fmha_bwd_dkdv_launch(const FuFmhaArgs* a, const float* lse2, const float* delta, int sq_pad, void* stream);
+int fu_fmha_bwd_fused_launch(const FuFmhaArgs* a, const float* lse2, const float* delta, int sq_pad, void* stream);
 
 extern "C" int fu_fmha_bwd(const FuFmhaArgs* a, void* stream_v)
 {
     if (!a || !a->q || !a->k || !a->v || !a->o || !a->lse || !a->d_o || !a->dq || !a->dk || !a->dv || !a->delta
-        || ((a->pad_ & 1) && !a->dq_acc)) {
+        || ((a->pad_ & 5) && !a->dq_acc)) {
         return fu::fail(FU_E_ARG, "fu_fmha_bwd: null operand");
     }
     if (a->head_dim != D) {
@@ -498,9 +499,23 @@ extern "C" int fu_fmha_bwd(const FuFmhaArgs* a, void* stream_v)
         FU_CUDA_OK(cudaGetLastError());
     }
     const bool single_pass = (a->pad_ & 1) != 0;
-    if (single_pass) {
+    const bool fused       = (a->pad_ & 4) != 0;
+    if (single_pass || fused) {
         FU_CUDA_OK(cudaMemsetAsync(a->dq_acc, 0,
                                    sizeof(float) * a->batch * static_cast<int64_t>(a->seq_q) * a->heads * D, stream));
+    }
+
+    auto round_dq = [&](float scale) -> int {
+        const int64_t n = static_cast<int64_t>(a->batch) * a->seq_q * a->heads * 16;
+        fmha_bwd_post_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, stream>>>(
+            a->dq_acc, static_cast<__nv_bfloat16*>(a->dq), a->q_row, a->q_head, a->q_batch, a->batch, a->heads, a->seq_q, scale);
+        FU_CUDA_OK(cudaGetLastError());
+        return FU_OK;
+    };
+    if (fused) {
+        // one software-pipelined pass (fmha_bwd_fused_sm100.cu); dQ is reduced in fp32
+        const int rc_f = fu_fmha_bwd_fused_launch(a, pre.lse2, pre.delta, sq_pad, stream_v);
+        return rc_f != FU_OK ? rc_f : round_dq(a->scale);
     }
 
     Params p{};
@@ -569,13 +584,7 @@ extern "C" int fu_fmha_bwd(const FuFmhaArgs* a, void* stream_v)
     }
     fmha_bwd_kernel<true><<<grid, THREADS, SMEM_BYTES, stream>>>(p);
     FU_CUDA_OK(cudaGetLastError());
-    {
-        const int64_t n = static_cast<int64_t>(a->batch) * a->seq_q * a->heads * 16;
-        fmha_bwd_post_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, stream>>>(
-            a->dq_acc, static_cast<__nv_bfloat16*>(a->dq), a->q_row, a->q_head, a->q_batch, a->batch, a->heads, a->seq_q);
-        FU_CUDA_OK(cudaGetLastError());
-    }
-    return FU_OK;
+    return round_dq(1.0f);
 }
 
 // ---- attention backward for callers that cannot allocate ------------------------------------------

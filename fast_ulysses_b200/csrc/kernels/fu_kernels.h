@@ -214,6 +214,9 @@ typedef struct FuFmhaArgs {
     void*       dv;
     float*      delta;   // fp32 scratch of 2 * batch * heads * roundup(seq_q, 128) floats
     float*      dq_acc;  // (batch, seq_q, heads, 128) fp32 scratch, zeroed by the launcher
+    // optional timeline of the fused backward: CTA 0 stores the SM clock of 16 pipeline events for
+    // each of its blocks 64..71 (128 words); null = no trace
+    uint64_t*   trace;
 } FuFmhaArgs;
 FU_API int fu_fmha_fwd(const FuFmhaArgs* args, void* stream);
 // d_o is addressed with o's strides, dq / dk / dv with q's / k's / v's strides.

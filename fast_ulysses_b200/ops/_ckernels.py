@@ -104,7 +104,7 @@ class FuFmhaArgs(C.Structure):
                 ("o_row", C.c_int64), ("o_head", C.c_int64), ("o_batch", C.c_int64),
                 ("ctas", C.c_int32), ("pad_", C.c_int32), ("err", C.c_void_p),
                 ("d_o", C.c_void_p), ("dq", C.c_void_p), ("dk", C.c_void_p), ("dv", C.c_void_p),
-                ("delta", C.c_void_p), ("dq_acc", C.c_void_p)]
+                ("delta", C.c_void_p), ("dq_acc", C.c_void_p), ("trace", C.c_void_p)]
 
 
 class FuPullArgs(C.Structure):

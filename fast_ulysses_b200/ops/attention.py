@@ -58,7 +58,7 @@ def attention_reference(q, k, v, scale=None):
 
 
 def fmha_bwd(q, k, v, o, lse, d_o, *, scale: float | None = None, ctas: int = 0, out=None,
-             single_pass: bool = False, variant: int = 0):
+             single_pass: bool = False, variant: int = 0, trace: torch.Tensor | None = None):
     """Gradients of ``fmha_fwd``. All tensors (b, s, h, 128) bf16; ``d_o`` must share ``o``'s
     strides. Returns ``(dq, dk, dv)`` shaped and strided like q, k, v (dense). The default runs
     two passes without atomics (dK/dV with the kv block stationary, dQ with the query rows
@@ -78,7 +78,8 @@ def fmha_bwd(q, k, v, o, lse, d_o, *, scale: float | None = None, ctas: int = 0,
     qc, kc, vc = (t if t.is_contiguous() else t.contiguous() for t in (q, k, v))
     sq_pad = (sq + 127) // 128 * 128
     stats = torch.empty(2 * b * h * sq_pad, dtype=torch.float32, device=q.device)
-    dq_acc = torch.empty(b, sq, h, d, dtype=torch.float32, device=q.device) if single_pass else None
+    needs_acc = single_pass or bool(variant & 4)
+    dq_acc = torch.empty(b, sq, h, d, dtype=torch.float32, device=q.device) if needs_acc else None
     a = ck.FuFmhaArgs()
     _fill(a, qc, kc, vc, o)
     a.lse = lse.data_ptr()
@@ -86,11 +87,11 @@ def fmha_bwd(q, k, v, o, lse, d_o, *, scale: float | None = None, ctas: int = 0,
     a.ctas = ctas
     a.d_o, a.dq, a.dk, a.dv = d_o.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
     a.delta = stats.data_ptr()
-    if single_pass:
+    if needs_acc:
         a.dq_acc = dq_acc.data_ptr()
-        a.pad_ = 1
-    elif variant:
-        a.pad_ = variant
+    a.pad_ = 1 if single_pass else variant
+    if trace is not None:  # int64[128] on the device: SM clock of 16 pipeline events for 8 blocks of CTA 0
+        a.trace = trace.data_ptr()
     ck.check(ck.lib().fu_fmha_bwd(C.byref(a), ck.stream_ptr()))
     return dq, dk, dv
 

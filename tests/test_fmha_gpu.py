@@ -80,7 +80,25 @@ def test_backward_matches_fp32_autograd(b, h, sq, skv):
     assert rel_err(v.grad, vr.grad) < 2e-2, ("dv", rel_err(v.grad, vr.grad))
 
 
-@pytest.mark.parametrize("single_pass", [False, True], ids=["two-pass", "single-pass"])
+@pytest.mark.parametrize("b,h,sq,skv", [(1, 1, 128, 128), (1, 2, 256, 384), (2, 2, 300, 500), (1, 1, 1000, 777)])
+def test_backward_fused_variant(b, h, sq, skv):
+    torch.manual_seed(sq + skv)
+    q = torch.randn(b, sq, h, 128, device="cuda").bfloat16()
+    k = torch.randn(b, skv, h, 128, device="cuda").bfloat16()
+    v = torch.randn(b, skv, h, 128, device="cuda").bfloat16()
+    o, lse = attention.fmha_fwd(q, k, v)
+    d_o = torch.randn_like(o)
+    dq, dk, dv = attention.fmha_bwd(q, k, v, o, lse, d_o, variant=4)
+    gemm.check_errors()
+    qr, kr, vr = (t.float().requires_grad_() for t in (q, k, v))
+    o_ref, _ = attention.attention_reference(qr, kr, vr)
+    o_ref.backward(d_o.float())
+    assert rel_err(dq, qr.grad) < 2e-2, ("dq", rel_err(dq, qr.grad))
+    assert rel_err(dk, kr.grad) < 2e-2, ("dk", rel_err(dk, kr.grad))
+    assert rel_err(dv, vr.grad) < 2e-2, ("dv", rel_err(dv, vr.grad))
+
+
+@pytest.mark.parametrize("single_pass", [False, True, 4], ids=["two-pass", "single-pass", "fused"])
 def test_backward_many_blocks_per_cta(single_pass):
     torch.manual_seed(1)
     q = torch.randn(1, 640, 3, 128, device="cuda").bfloat16()
@@ -88,7 +106,8 @@ def test_backward_many_blocks_per_cta(single_pass):
     v = torch.randn(1, 900, 3, 128, device="cuda").bfloat16()
     o, lse = attention.fmha_fwd(q, k, v)
     d_o = torch.randn_like(o)
-    dq, dk, dv = attention.fmha_bwd(q, k, v, o, lse, d_o, ctas=2, single_pass=single_pass)
+    kw = {"variant": 4} if single_pass == 4 else {"single_pass": single_pass}
+    dq, dk, dv = attention.fmha_bwd(q, k, v, o, lse, d_o, ctas=2, **kw)
     gemm.check_errors()
     qr, kr, vr = (t.float().requires_grad_() for t in (q, k, v))
     o_ref, _ = attention.attention_reference(qr, kr, vr)
