@@ -61,7 +61,6 @@ struct Params {
     int            n_q, kv_blocks, total_work;
     float          scale, scale_log2;
     uint32_t*      err;
-    int            dbg;
     uint64_t*      trace;
 };
 
@@ -85,6 +84,14 @@ __device__ __forceinline__ void stamp(const Params& p, uint32_t it, int ev)
     if (p.trace && blockIdx.x == 0 && it >= 64u && it < 72u) {
         p.trace[(it - 64u) * 16 + ev] = clock64();
     }
+}
+
+// CTAs that run at the same time own neighbouring K/V blocks of one head. Each starts its sweep
+// over the query blocks at a different block, so that their dQ reductions do not all land on the
+// same addresses at the same moment.
+__device__ __forceinline__ int first_block(const Params& p, int jb)
+{
+    return static_cast<int>(static_cast<int64_t>(jb) * p.n_q / p.kv_blocks);
 }
 
 __device__ __forceinline__ void red_add(float* addr, float v)
@@ -191,7 +198,9 @@ __global__ void __launch_bounds__(THREADS, 1) fmha_bwd_fused_kernel(const __grid
                 }
                 const float* lse2  = p.lse2 + (static_cast<int64_t>(b) * p.H + h) * p.Sq_pad;
                 const float* delta = p.delta + (static_cast<int64_t>(b) * p.H + h) * p.Sq_pad;
-                for (int i = 0; i < n_q; ++i, ++it) {
+                const int    first = first_block(p, jb);
+                for (int i0 = 0; i0 < n_q; ++i0, ++it) {
+                    const int      i  = i0 + first < n_q ? i0 + first : i0 + first - n_q;
                     const int      s  = it % STAGES;
                     const uint32_t ph = ((it / STAGES) & 1u) ^ 1u;
                     uint8_t*       ss = sm + OFF_STATS + s * 1024;
@@ -464,7 +473,9 @@ __global__ void __launch_bounds__(THREADS, 1) fmha_bwd_fused_kernel(const __grid
             const int h  = (w / p.kv_blocks) % p.H;
             const int b  = w / (p.kv_blocks * p.H);
             float*    dq = p.dq_acc + (static_cast<int64_t>(b) * p.Sq * p.H + h) * D + dcol;
-            for (int i = 0; i < n_q; ++i, ++it) {
+            const int first = first_block(p, w % p.kv_blocks);
+            for (int i0 = 0; i0 < n_q; ++i0, ++it) {
+                const int i = i0 + first < n_q ? i0 + first : i0 + first - n_q;
                 if (!ptx::mbar_wait(&bar.dq_full, it & 1u)) {
                     flag(p, ERR_DRAIN);
                     ok = false;
@@ -483,31 +494,19 @@ __global__ void __launch_bounds__(THREADS, 1) fmha_bwd_fused_kernel(const __grid
                 if (threadIdx.x == 320) {
                     stamp(p, it, 10);
                 }
-                if (p.dbg & 1) {
-                    continue;
-                }
                 const int q0    = i * BLK + qh * 64;
                 const int valid = p.Sq - q0;  // query rows of this half that exist
                 float*    row   = dq + static_cast<int64_t>(q0) * q_stride;
-                if (valid >= 64) {
 #pragma unroll
-                    for (int k = 0; k < 32; ++k) {
+                for (int k = 0; k < 32; ++k) {
+                    if (k < valid) {
                         red_add(row + k * q_stride, __uint_as_float(r0[k]));
                     }
-#pragma unroll
-                    for (int k = 0; k < 32; ++k) {
-                        red_add(row + (32 + k) * q_stride, __uint_as_float(r1[k]));
-                    }
                 }
-                else {
 #pragma unroll
-                    for (int k = 0; k < 32; ++k) {
-                        if (k < valid) {
-                            red_add(row + k * q_stride, __uint_as_float(r0[k]));
-                        }
-                        if (32 + k < valid) {
-                            red_add(row + (32 + k) * q_stride, __uint_as_float(r1[k]));
-                        }
+                for (int k = 0; k < 32; ++k) {
+                    if (32 + k < valid) {
+                        red_add(row + (32 + k) * q_stride, __uint_as_float(r1[k]));
                     }
                 }
             }
@@ -563,7 +562,6 @@ int fu_fmha_bwd_fused_launch(const FuFmhaArgs* a, const float* lse2, const float
     p.scale      = a->scale;
     p.scale_log2 = a->scale * 1.4426950408889634f;
     p.err        = a->err;
-    p.dbg        = (a->pad_ >> 8) & 0xff;
     p.trace      = a->trace;
     int dev = 0, sms = 0;
     FU_CUDA_OK(cudaGetDevice(&dev));

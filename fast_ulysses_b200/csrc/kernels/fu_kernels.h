@@ -191,6 +191,9 @@ FU_API int fu_pull_outproj(const FuPullArgs* args, void* stream);
 // and batch axes, so both the window layout (b, s, h, d) and (b, h, s, d) work without a copy.
 // lse (nullable) is (batch, heads, seq_q) fp32, natural log. do/dq/dk/dv follow the layout of
 // o/q/k/v respectively; delta and dq_acc are scratch the caller provides for the backward.
+// Backward: two passes without atomics (bit-reproducible dQ, about 1.5x the time of the default
+// single pass, which sums dQ over the K/V blocks with fp32 reductions).
+enum { FU_FMHA_DETERMINISTIC = 1 };
 typedef struct FuFmhaArgs {
     const void* q;
     const void* k;
@@ -204,8 +207,7 @@ typedef struct FuFmhaArgs {
     int64_t     v_row, v_head, v_batch;
     int64_t     o_row, o_head, o_batch;
     int32_t     ctas;
-    int32_t     pad_;    // backward: bit 0 selects the single-pass variant (dQ by atomic reductions
-                         // into dq_acc); 0 = two passes without atomics, dq_acc unused
+    int32_t     flags;   // backward: FU_FMHA_* bits
     uint32_t*   err;
     // backward only
     const void* d_o;
@@ -213,7 +215,8 @@ typedef struct FuFmhaArgs {
     void*       dk;
     void*       dv;
     float*      delta;   // fp32 scratch of 2 * batch * heads * roundup(seq_q, 128) floats
-    float*      dq_acc;  // (batch, seq_q, heads, 128) fp32 scratch, zeroed by the launcher
+    float*      dq_acc;  // (batch, seq_q, heads, 128) fp32 scratch, zeroed by the launcher; not needed
+                         // (may be null) with FU_FMHA_DETERMINISTIC
     // optional timeline of the fused backward: CTA 0 stores the SM clock of 16 pipeline events for
     // each of its blocks 64..71 (128 words); null = no trace
     uint64_t*   trace;

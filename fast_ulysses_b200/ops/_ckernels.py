@@ -102,7 +102,7 @@ class FuFmhaArgs(C.Structure):
                 ("k_row", C.c_int64), ("k_head", C.c_int64), ("k_batch", C.c_int64),
                 ("v_row", C.c_int64), ("v_head", C.c_int64), ("v_batch", C.c_int64),
                 ("o_row", C.c_int64), ("o_head", C.c_int64), ("o_batch", C.c_int64),
-                ("ctas", C.c_int32), ("pad_", C.c_int32), ("err", C.c_void_p),
+                ("ctas", C.c_int32), ("flags", C.c_int32), ("err", C.c_void_p),
                 ("d_o", C.c_void_p), ("dq", C.c_void_p), ("dk", C.c_void_p), ("dv", C.c_void_p),
                 ("delta", C.c_void_p), ("dq_acc", C.c_void_p), ("trace", C.c_void_p)]
 

@@ -58,11 +58,13 @@ def attention_reference(q, k, v, scale=None):
 
 
 def fmha_bwd(q, k, v, o, lse, d_o, *, scale: float | None = None, ctas: int = 0, out=None,
-             single_pass: bool = False, variant: int = 0, trace: torch.Tensor | None = None):
+             deterministic: bool = False, trace: torch.Tensor | None = None):
     """Gradients of ``fmha_fwd``. All tensors (b, s, h, 128) bf16; ``d_o`` must share ``o``'s
-    strides. Returns ``(dq, dk, dv)`` shaped and strided like q, k, v (dense). The default runs
-    two passes without atomics (dK/dV with the kv block stationary, dQ with the query rows
-    stationary); ``single_pass=True`` runs the one-kernel variant that reduces dQ atomically."""
+    strides. Returns ``(dq, dk, dv)`` shaped and strided like q, k, v (dense). The default is one
+    software-pipelined pass that sums dQ over the K/V blocks with fp32 reductions (dK and dV are
+    bit-reproducible, dQ to rounding); ``deterministic=True`` runs two passes without atomics
+    (dK/dV with the K/V block stationary, then dQ with the query rows stationary) at about 1.5x
+    the time."""
     b, sq, h, d = q.shape
     if d_o.stride() != o.stride():
         d_o = d_o.contiguous()
@@ -78,8 +80,7 @@ def fmha_bwd(q, k, v, o, lse, d_o, *, scale: float | None = None, ctas: int = 0,
     qc, kc, vc = (t if t.is_contiguous() else t.contiguous() for t in (q, k, v))
     sq_pad = (sq + 127) // 128 * 128
     stats = torch.empty(2 * b * h * sq_pad, dtype=torch.float32, device=q.device)
-    needs_acc = single_pass or bool(variant & 4)
-    dq_acc = torch.empty(b, sq, h, d, dtype=torch.float32, device=q.device) if needs_acc else None
+    dq_acc = None if deterministic else torch.empty(b, sq, h, d, dtype=torch.float32, device=q.device)
     a = ck.FuFmhaArgs()
     _fill(a, qc, kc, vc, o)
     a.lse = lse.data_ptr()
@@ -87,9 +88,9 @@ def fmha_bwd(q, k, v, o, lse, d_o, *, scale: float | None = None, ctas: int = 0,
     a.ctas = ctas
     a.d_o, a.dq, a.dk, a.dv = d_o.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
     a.delta = stats.data_ptr()
-    if needs_acc:
+    if dq_acc is not None:
         a.dq_acc = dq_acc.data_ptr()
-    a.pad_ = 1 if single_pass else variant
+    a.flags = 1 if deterministic else 0
     if trace is not None:  # int64[128] on the device: SM clock of 16 pipeline events for 8 blocks of CTA 0
         a.trace = trace.data_ptr()
     ck.check(ck.lib().fu_fmha_bwd(C.byref(a), ck.stream_ptr()))

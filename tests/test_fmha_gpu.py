@@ -81,15 +81,17 @@ def test_backward_matches_fp32_autograd(b, h, sq, skv):
 
 
 @pytest.mark.parametrize("b,h,sq,skv", [(1, 1, 128, 128), (1, 2, 256, 384), (2, 2, 300, 500), (1, 1, 1000, 777)])
-def test_backward_fused_variant(b, h, sq, skv):
+def test_backward_deterministic_two_pass(b, h, sq, skv):
     torch.manual_seed(sq + skv)
     q = torch.randn(b, sq, h, 128, device="cuda").bfloat16()
     k = torch.randn(b, skv, h, 128, device="cuda").bfloat16()
     v = torch.randn(b, skv, h, 128, device="cuda").bfloat16()
     o, lse = attention.fmha_fwd(q, k, v)
     d_o = torch.randn_like(o)
-    dq, dk, dv = attention.fmha_bwd(q, k, v, o, lse, d_o, variant=4)
+    dq, dk, dv = attention.fmha_bwd(q, k, v, o, lse, d_o, deterministic=True)
+    again = attention.fmha_bwd(q, k, v, o, lse, d_o, deterministic=True)
     gemm.check_errors()
+    assert all(torch.equal(x, y) for x, y in zip((dq, dk, dv), again))
     qr, kr, vr = (t.float().requires_grad_() for t in (q, k, v))
     o_ref, _ = attention.attention_reference(qr, kr, vr)
     o_ref.backward(d_o.float())
@@ -98,16 +100,15 @@ def test_backward_fused_variant(b, h, sq, skv):
     assert rel_err(dv, vr.grad) < 2e-2, ("dv", rel_err(dv, vr.grad))
 
 
-@pytest.mark.parametrize("single_pass", [False, True, 4], ids=["two-pass", "single-pass", "fused"])
-def test_backward_many_blocks_per_cta(single_pass):
+@pytest.mark.parametrize("deterministic", [False, True], ids=["single-pass", "two-pass"])
+def test_backward_many_blocks_per_cta(deterministic):
     torch.manual_seed(1)
     q = torch.randn(1, 640, 3, 128, device="cuda").bfloat16()
     k = torch.randn(1, 900, 3, 128, device="cuda").bfloat16()
     v = torch.randn(1, 900, 3, 128, device="cuda").bfloat16()
     o, lse = attention.fmha_fwd(q, k, v)
     d_o = torch.randn_like(o)
-    kw = {"variant": 4} if single_pass == 4 else {"single_pass": single_pass}
-    dq, dk, dv = attention.fmha_bwd(q, k, v, o, lse, d_o, ctas=2, **kw)
+    dq, dk, dv = attention.fmha_bwd(q, k, v, o, lse, d_o, ctas=2, deterministic=deterministic)
     gemm.check_errors()
     qr, kr, vr = (t.float().requires_grad_() for t in (q, k, v))
     o_ref, _ = attention.attention_reference(qr, kr, vr)
