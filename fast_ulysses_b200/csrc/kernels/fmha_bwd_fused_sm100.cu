@@ -4,10 +4,10 @@
 // 128-row query blocks i. Five products per block pair, everything transposed so that the kv row
 // sits on the TMEM lane axis and the probabilities can be fed back as the A operand:
 //   S^T(i)  = K Q_i^T            (SS)      C1: P^T = exp2(S^T c - lse)               -> TMEM (bf16)
-//   dP^T(i) = V dO_i^T           (SS)      C2: dS^T = P^T o (dP^T - delta) scale     -> TMEM + smem
+//   dP^T(i) = V dO_i^T           (SS)      C2: dS^T = P^T o (dP^T - delta)           -> TMEM + smem
 //   dV     += P^T dO_i           (A from TMEM)
 //   dK     += dS^T Q_i           (A from TMEM)
-//   dQ_i^T  = K^T dS^T           (SS, both operands MN-major); drained by four extra warps with
+//   dQ_i^T  = K^T dS^T           (SS, both operands MN-major); drained by eight extra warps with
 //                                coalesced fp32 reductions into a global accumulator
 // Tensor memory: S^T/P^T | dP^T/dS^T/dQ^T | dV | dK, 128 fp32 columns each (all 512).
 //
@@ -16,6 +16,12 @@
 // the drain warps copy them to registers, release the columns at once and only then issue their
 // reductions, which overlap the next block. The softmax scale is applied to dK in the epilogue and
 // to dQ when the accumulator is rounded, not to every element of dS.
+//
+// Measured limits (S = 32768, 5 heads, SM clock counter): a 128x128x16 MMA takes 64 clocks when its
+// descriptors are ready (8 per product: 512), a tensor-memory load-and-wait about 200, and the fp32
+// reductions of all SMs together move about 3.5 TB/s into L2, which bounds this algorithm near
+// 1.1 PFLOP/s (64 KiB of reductions per 21 MFLOP). The dependent chain
+// dP -> C2 -> dK, dQ -> drain -> dP is what sets the period, not the tensor pipe.
 // Warps: 0 = TMA producer, 1 = MMA issuer, 2..9 = two threads per kv row, 10..17 = dQ drain.
 #include "fu_kernels.h"
 #include "host_util.h"
@@ -118,14 +124,13 @@ template <int C>
 __device__ __forceinline__ void c2_chunk(const uint32_t (&r)[16], const uint32_t (&pk)[32], const float* delta,
                                          uint32_t t_dp, uint8_t* ds_row, int row_in)
 {
+    // the difference in fp32 (it cancels), the product with the bf16 probabilities as a packed pair
     uint32_t dd[8];
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
-        const uint32_t w  = pk[C * 8 + k];
-        const float    p0 = __uint_as_float(w << 16), p1 = __uint_as_float(w & 0xffff0000u);
-        const float    d0 = p0 * (__uint_as_float(r[2 * k]) - delta[C * 16 + 2 * k]);
-        const float    d1 = p1 * (__uint_as_float(r[2 * k + 1]) - delta[C * 16 + 2 * k + 1]);
-        dd[k]             = ptx::pack_bf16x2(d0, d1);
+        const float d0 = __uint_as_float(r[2 * k]) - delta[C * 16 + 2 * k];
+        const float d1 = __uint_as_float(r[2 * k + 1]) - delta[C * 16 + 2 * k + 1];
+        dd[k]          = ptx::mul_bf16x2(pk[C * 8 + k], ptx::pack_bf16x2(d0, d1));
     }
     ptx::tmem_st_32x8(t_dp + C * 8, dd);
     *reinterpret_cast<uint4*>(ds_row + (((2 * C) ^ (row_in & 7)) << 4))     = make_uint4(dd[0], dd[1], dd[2], dd[3]);
@@ -156,12 +161,12 @@ __global__ void __launch_bounds__(THREADS, 1) fmha_bwd_fused_kernel(const __grid
         }
         ptx::mbar_init(&bar.s_full, 1);
         ptx::mbar_init(&bar.dp_full, 1);
-        ptx::mbar_init(&bar.p_ready, 256);
-        ptx::mbar_init(&bar.ds_ready, 256);
+        ptx::mbar_init(&bar.p_ready, 8);  // one arrival per warp
+        ptx::mbar_init(&bar.ds_ready, 8);  // one arrival per warp
         ptx::mbar_init(&bar.dq_full, 1);
-        ptx::mbar_init(&bar.dq_free, 256);
+        ptx::mbar_init(&bar.dq_free, 8);  // one arrival per warp
         ptx::mbar_init(&bar.acc_full, 1);
-        ptx::mbar_init(&bar.acc_free, 256);
+        ptx::mbar_init(&bar.acc_free, 8);  // one arrival per warp
         ptx::mbar_fence_init();
         ptx::tma_prefetch_desc(&p.map_q);
         ptx::tma_prefetch_desc(&p.map_k);
@@ -234,15 +239,23 @@ __global__ void __launch_bounds__(THREADS, 1) fmha_bwd_fused_kernel(const __grid
             constexpr uint32_t idesc_kk = ptx::make_idesc(1, 1, BLK, BLK, 0, 0);  // A, B K-major
             constexpr uint32_t idesc_tn = ptx::make_idesc(1, 1, BLK, D, 0, 1);    // A from TMEM, B MN-major
             constexpr uint32_t idesc_nn = ptx::make_idesc(1, 1, D, BLK, 1, 1);    // A, B MN-major
-            const uint32_t     ka = base + OFF_K, va = base + OFF_V, dsa = base + OFF_DS;
+            // one descriptor per operand and role, built once; every MMA below only steps it
+            const uint64_t k_kmaj  = ptx::smem_desc_sw128(base + OFF_K, 16, 1024);
+            const uint64_t v_kmaj  = ptx::smem_desc_sw128(base + OFF_V, 16, 1024);
+            const uint64_t q_kmaj  = ptx::smem_desc_sw128(base + OFF_Q, 16, 1024);
+            const uint64_t do_kmaj = ptx::smem_desc_sw128(base + OFF_DO, 16, 1024);
+            const uint64_t k_mn    = ptx::smem_desc_sw128(base + OFF_K, HALF_BYTES, 1024);
+            const uint64_t q_mn    = ptx::smem_desc_sw128(base + OFF_Q, HALF_BYTES, 1024);
+            const uint64_t do_mn   = ptx::smem_desc_sw128(base + OFF_DO, HALF_BYTES, 1024);
+            const uint64_t ds_mn   = ptx::smem_desc_sw128(base + OFF_DS, HALF_BYTES, 1024);
             uint32_t           it = 0, wc = 0;
             bool               ok = true;
-            auto issue_s = [&](uint32_t qa) {  // S^T = K Q^T
+            auto issue_s = [&](int stage) {  // S^T = K Q^T
+                const uint64_t qd = ptx::desc_advance(q_kmaj, stage * TILE_BYTES);
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
                     const uint32_t off = (kk >> 2) * HALF_BYTES + (kk & 3) * 32;
-                    ptx::mma_f16_ss(tmem, ptx::smem_desc_sw128(ka + off, 16, 1024), ptx::smem_desc_sw128(qa + off, 16, 1024),
-                                    idesc_kk, kk != 0);
+                    ptx::mma_f16_ss(tmem, ptx::desc_advance(k_kmaj, off), ptx::desc_advance(qd, off), idesc_kk, kk != 0);
                 }
                 ptx::mma_commit(&bar.s_full);
             };
@@ -252,12 +265,13 @@ __global__ void __launch_bounds__(THREADS, 1) fmha_bwd_fused_kernel(const __grid
                     break;
                 }
                 ptx::tc_fence_after();
-                issue_s(base + OFF_Q + (it % STAGES) * TILE_BYTES);
+                issue_s(it % STAGES);
                 for (int i = 0; i < n_q; ++i, ++it) {
                     const int      s  = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1u;
-                    const uint32_t qa = base + OFF_Q + s * TILE_BYTES;
-                    const uint32_t oa = base + OFF_DO + s * TILE_BYTES;
+                    const uint64_t o_k = ptx::desc_advance(do_kmaj, s * TILE_BYTES);
+                    const uint64_t o_m = ptx::desc_advance(do_mn, s * TILE_BYTES);
+                    const uint64_t q_m = ptx::desc_advance(q_mn, s * TILE_BYTES);
                     // the previous block's dQ^T must have left the columns dP^T is written to
                     if (!ptx::mbar_wait(&bar.do_full[s], ph) || !ptx::mbar_wait(&bar.dq_free, (it & 1u) ^ 1u)) {
                         flag(p, ERR_MMA);
@@ -269,8 +283,8 @@ __global__ void __launch_bounds__(THREADS, 1) fmha_bwd_fused_kernel(const __grid
 #pragma unroll
                     for (int kk = 0; kk < D / 16; ++kk) {  // dP^T = V dO^T
                         const uint32_t off = (kk >> 2) * HALF_BYTES + (kk & 3) * 32;
-                        ptx::mma_f16_ss(tmem + 128, ptx::smem_desc_sw128(va + off, 16, 1024),
-                                        ptx::smem_desc_sw128(oa + off, 16, 1024), idesc_kk, kk != 0);
+                        ptx::mma_f16_ss(tmem + 128, ptx::desc_advance(v_kmaj, off), ptx::desc_advance(o_k, off), idesc_kk,
+                                        kk != 0);
                     }
                     ptx::mma_commit(&bar.dp_full);
                     if (!ptx::mbar_wait(&bar.p_ready, it & 1u)
@@ -283,9 +297,8 @@ __global__ void __launch_bounds__(THREADS, 1) fmha_bwd_fused_kernel(const __grid
                     stamp(p, it, 0);
 #pragma unroll
                     for (int kk = 0; kk < BLK / 16; ++kk) {  // dV += P^T dO   (contraction over q)
-                        ptx::mma_f16_ts(tmem + 256, tmem + (kk >> 2) * 64 + (kk & 3) * 8,
-                                        ptx::smem_desc_sw128(oa + kk * 2048, HALF_BYTES, 1024), idesc_tn,
-                                        i != 0 || kk != 0);
+                        ptx::mma_f16_ts(tmem + 256, tmem + (kk >> 2) * 64 + (kk & 3) * 8, ptx::desc_advance(o_m, kk * 2048),
+                                        idesc_tn, i != 0 || kk != 0);
                     }
                     if (i + 1 < n_q) {
                         const uint32_t n = it + 1;
@@ -295,7 +308,7 @@ __global__ void __launch_bounds__(THREADS, 1) fmha_bwd_fused_kernel(const __grid
                             break;
                         }
                         ptx::tc_fence_after();
-                        issue_s(base + OFF_Q + (n % STAGES) * TILE_BYTES);
+                        issue_s(n % STAGES);
                     }
                     stamp(p, it, 2);
                     if (!ptx::mbar_wait(&bar.ds_ready, it & 1u)) {
@@ -308,14 +321,13 @@ __global__ void __launch_bounds__(THREADS, 1) fmha_bwd_fused_kernel(const __grid
 #pragma unroll
                     for (int kk = 0; kk < BLK / 16; ++kk) {  // dK += dS^T Q
                         ptx::mma_f16_ts(tmem + 384, tmem + 128 + (kk >> 2) * 64 + (kk & 3) * 8,
-                                        ptx::smem_desc_sw128(qa + kk * 2048, HALF_BYTES, 1024), idesc_tn,
-                                        i != 0 || kk != 0);
+                                        ptx::desc_advance(q_m, kk * 2048), idesc_tn, i != 0 || kk != 0);
                     }
                     ptx::mma_commit(&bar.empty[s]);
 #pragma unroll
                     for (int kk = 0; kk < BLK / 16; ++kk) {  // dQ^T = K^T dS^T   (contraction over kv)
-                        ptx::mma_f16_ss(tmem + 128, ptx::smem_desc_sw128(ka + kk * 2048, HALF_BYTES, 1024),
-                                        ptx::smem_desc_sw128(dsa + kk * 2048, HALF_BYTES, 1024), idesc_nn, kk != 0);
+                        ptx::mma_f16_ss(tmem + 128, ptx::desc_advance(k_mn, kk * 2048), ptx::desc_advance(ds_mn, kk * 2048),
+                                        idesc_nn, kk != 0);
                     }
                     ptx::mma_commit(&bar.dq_full);
                     stamp(p, it, 4);
@@ -381,7 +393,7 @@ __global__ void __launch_bounds__(THREADS, 1) fmha_bwd_fused_kernel(const __grid
                 }
                 ptx::tmem_st_wait();
                 ptx::tc_fence_before();
-                ptx::mbar_arrive(&bar.p_ready);
+                ptx::mbar_arrive_warp(&bar.p_ready);
                 if (threadIdx.x == 64) {
                     stamp(p, it, 6);
                 }
@@ -413,7 +425,7 @@ __global__ void __launch_bounds__(THREADS, 1) fmha_bwd_fused_kernel(const __grid
                 ptx::tmem_st_wait();
                 ptx::fence_proxy_async_smem();
                 ptx::tc_fence_before();
-                ptx::mbar_arrive(&bar.ds_ready);
+                ptx::mbar_arrive_warp(&bar.ds_ready);
                 if (threadIdx.x == 64) {
                     stamp(p, it, 8);
                 }
@@ -453,7 +465,7 @@ __global__ void __launch_bounds__(THREADS, 1) fmha_bwd_fused_kernel(const __grid
                 }
             }
             ptx::tc_fence_before();
-            ptx::mbar_arrive(&bar.acc_free);
+            ptx::mbar_arrive_warp(&bar.acc_free);
         }
     }
     else {
@@ -490,7 +502,7 @@ __global__ void __launch_bounds__(THREADS, 1) fmha_bwd_fused_kernel(const __grid
                 ptx::tmem_ld_32x32(t_dq + 32, r1);
                 ptx::tmem_ld_wait();
                 ptx::tc_fence_before();
-                ptx::mbar_arrive(&bar.dq_free);
+                ptx::mbar_arrive_warp(&bar.dq_free);
                 if (threadIdx.x == 320) {
                     stamp(p, it, 10);
                 }

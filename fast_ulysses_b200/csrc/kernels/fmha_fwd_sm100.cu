@@ -96,9 +96,9 @@ __global__ void __launch_bounds__(THREADS, 1) fmha_fwd_kernel(const __grid_const
         }
         for (int t = 0; t < QT; ++t) {
             ptx::mbar_init(&bar.s_full[t], 1);
-            ptx::mbar_init(&bar.p_ready[t], 128);
+            ptx::mbar_init(&bar.p_ready[t], 4);  // one arrival per warp
             ptx::mbar_init(&bar.o_final[t], 1);
-            ptx::mbar_init(&bar.o_free[t], 128);
+            ptx::mbar_init(&bar.o_free[t], 4);
         }
         ptx::mbar_fence_init();
         ptx::tma_prefetch_desc(&p.map_q);
@@ -172,26 +172,30 @@ __global__ void __launch_bounds__(THREADS, 1) fmha_fwd_kernel(const __grid_const
             uint32_t           pcount[QT] = {0, 0};
             bool               ok = true;
 
+            // one descriptor per operand, built once; every MMA below only steps it
+            const uint64_t desc_q = ptx::smem_desc_sw128(sq_addr, 16, 1024);
+            const uint64_t desc_k = ptx::smem_desc_sw128(sk_addr, 16, 1024);
+            const uint64_t desc_v = ptx::smem_desc_sw128(sv_addr, HALF_BYTES, 1024);
+
             auto issue_qk = [&](int t, int stage) {
-                const uint32_t qa = sq_addr + t * TILE_BYTES;
-                const uint32_t ka = sk_addr + stage * TILE_BYTES;
+                const uint64_t qa = ptx::desc_advance(desc_q, t * TILE_BYTES);
+                const uint64_t ka = ptx::desc_advance(desc_k, stage * TILE_BYTES);
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
                     const uint32_t off = (kk >> 2) * HALF_BYTES + (kk & 3) * 32;
-                    ptx::mma_f16_ss(tmem + t * 128, ptx::smem_desc_sw128(qa + off, 16, 1024),
-                                    ptx::smem_desc_sw128(ka + off, 16, 1024), idesc_qk, kk != 0);
+                    ptx::mma_f16_ss(tmem + t * 128, ptx::desc_advance(qa, off), ptx::desc_advance(ka, off), idesc_qk,
+                                    kk != 0);
                 }
                 ptx::mma_commit(&bar.s_full[t]);
             };
             auto issue_pv = [&](int t, int stage, bool accumulate) {
-                const uint32_t va = sv_addr + stage * TILE_BYTES;
+                // 16 kv rows = 2048 bytes further down; the two 64-wide halves of d are HALF_BYTES
+                // apart (leading byte offset), 8-row groups 1024 bytes apart
+                const uint64_t va = ptx::desc_advance(desc_v, stage * TILE_BYTES);
 #pragma unroll
                 for (int kk = 0; kk < BN / 16; ++kk) {
-                    // 16 kv rows = 2048 bytes further down; the two 64-wide halves of d are
-                    // HALF_BYTES apart (leading byte offset), 8-row groups 1024 bytes apart
-                    ptx::mma_f16_ts(tmem + 256 + t * 128, tmem + t * 128 + kk * 8,
-                                    ptx::smem_desc_sw128(va + kk * 2048, HALF_BYTES, 1024), idesc_pv,
-                                    accumulate || kk != 0);
+                    ptx::mma_f16_ts(tmem + 256 + t * 128, tmem + t * 128 + kk * 8, ptx::desc_advance(va, kk * 2048),
+                                    idesc_pv, accumulate || kk != 0);
                 }
             };
 
@@ -351,7 +355,7 @@ __global__ void __launch_bounds__(THREADS, 1) fmha_fwd_kernel(const __grid_const
                 l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
                 ptx::tmem_st_wait();
                 ptx::tc_fence_before();
-                ptx::mbar_arrive(&bar.p_ready[t]);
+                ptx::mbar_arrive_warp(&bar.p_ready[t]);
             }
             if (!ok) {
                 break;
@@ -387,7 +391,7 @@ __global__ void __launch_bounds__(THREADS, 1) fmha_fwd_kernel(const __grid_const
                 p.lse[(static_cast<int64_t>(b) * p.H + h) * p.Sq + row] = (m_ref * c + ptx::lg2(l)) * 0.6931471805599453f;
             }
             ptx::tc_fence_before();
-            ptx::mbar_arrive(&bar.o_free[t]);
+            ptx::mbar_arrive_warp(&bar.o_free[t]);
         }
     }
 

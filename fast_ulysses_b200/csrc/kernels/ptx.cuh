@@ -104,6 +104,17 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar)
 {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
 }
+// One arrival for a whole warp: every lane has finished and fenced its part, the warp converges,
+// lane 0 arrives (initialise the barrier with the number of WARPS). An arrival is a shared-memory
+// atomic: one per thread of an 8-warp group serialises into several hundred clocks on the path
+// between two MMAs, one per warp does not.
+__device__ __forceinline__ void mbar_arrive_warp(uint64_t* bar)
+{
+    __syncwarp();
+    if ((threadIdx.x & 31u) == 0u) {
+        mbar_arrive(bar);
+    }
+}
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity)
 {
     uint32_t ok;
@@ -331,6 +342,12 @@ __device__ __forceinline__ void tmem_st_32x8(uint32_t taddr, const uint32_t (&r)
                  : "memory");
 }
 
+__device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b)
+{
+    uint32_t r;
+    asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
 __device__ __forceinline__ float ex2(float x)
 {
     float y;
@@ -379,6 +396,17 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr, uint32_t lbo
     d |= 1ull << 46;  // descriptor version for sm_100
     d |= 2ull << 61;  // 128-byte swizzle
     return d;
+}
+
+// The start address sits in the low bits of a descriptor in 16-byte units, so moving an operand
+// along K, to the other 64-column half or to another pipeline stage is one integer add. The issuing
+// thread is a single warp whose dependent instructions cannot overlap: building a descriptor from
+// scratch for every instruction (mask, shift, three ORs, twice) costs more than the 64 clocks a
+// 128x128x16 MMA takes, and the tensor pipe then waits for its issuer. Build each operand's
+// descriptor once, outside the loop, and step it with this.
+__device__ __forceinline__ uint64_t desc_advance(uint64_t desc, uint32_t bytes)
+{
+    return desc + static_cast<uint64_t>(bytes >> 4);
 }
 
 // Instruction descriptor for kind::f16 / kind::f8f6f4 with fp32 accumulation.

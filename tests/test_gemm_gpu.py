@@ -70,3 +70,20 @@ def test_linear_autograd():
     assert rel_err(x.grad, xr.grad) < 6e-3
     assert rel_err(w.grad, wr.grad) < 6e-3
     assert rel_err(bias.grad, br.grad) < 6e-3
+
+
+@pytest.mark.parametrize("tokens", [9450, 75, 1001])
+def test_linear_autograd_with_a_token_count_that_is_not_a_multiple_of_8(tokens):
+    # the weight gradient contracts over the tokens: 75600 / 8 ranks = 9450 rows per rank
+    torch.manual_seed(tokens)
+    x = (torch.randn(tokens, 256, device="cuda") * 0.5).bfloat16().requires_grad_()
+    w = (torch.randn(384, 256, device="cuda") * 0.1).bfloat16().requires_grad_()
+    b = torch.randn(384, device="cuda").bfloat16().requires_grad_()
+    y = gemm.linear(x, w, b)
+    gy = torch.randn_like(y)
+    y.backward(gy)
+    gemm.check_errors()
+    xr, wr, br = (t.detach().float().requires_grad_() for t in (x, w, b))
+    torch.nn.functional.linear(xr, wr, br).backward(gy.float())
+    assert rel_err(y, torch.nn.functional.linear(xr, wr, br)) < 1e-2
+    assert rel_err(x.grad, xr.grad) < 1e-2 and rel_err(w.grad, wr.grad) < 1e-2 and rel_err(b.grad, br.grad) < 1e-2
