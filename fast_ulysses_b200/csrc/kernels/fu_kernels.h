@@ -94,6 +94,10 @@ FU_API int fu_barrier(FuCtrl* const* peer_ctrl, int rank, int world, uint32_t ti
 // C[m,n] = act(A[m,k] * B[n,k]^T + bias[n]) + residual[m,n]; bf16 operands, fp32 accumulation.
 // act: 0 none, 1 GELU (tanh form), 2 GELU (erf form). `err` (nullable) is a device word that
 // receives a non-zero code if a wait inside the kernel ran out.
+// flags: an operand may be given with the contraction along its rows instead of its columns
+// (A stored k x m with pitch lda, B stored k x n with pitch ldb). The weight gradient of a linear
+// layer, dW = dY^T X, is then a GEMM over dY and X as they lie in memory.
+enum { FU_GEMM_A_KM = 1, FU_GEMM_B_KN = 2 };
 typedef struct FuGemmArgs {
     const void*  a;
     const void*  b;
@@ -104,6 +108,7 @@ typedef struct FuGemmArgs {
     int32_t      act;
     int32_t      ctas;
     uint32_t*    err;
+    int32_t      flags;
 } FuGemmArgs;
 FU_API int fu_gemm_bf16(const FuGemmArgs* args, void* stream);
 

@@ -465,18 +465,20 @@ int set_smem(K kernel)
 }
 
 int fill_core(Core& core, const void* a, const void* b, int64_t m, int64_t n, int64_t k, int64_t lda, int64_t ldb,
-              uint32_t* err)
+              uint32_t* err, int flags = 0)
 {
     if (m <= 0 || n <= 0 || k <= 0) {
         return fu::fail(FU_E_ARG, "gemm: empty problem (m=%lld n=%lld k=%lld)", (long long)m, (long long)n, (long long)k);
     }
     // K itself may be anything (TMA zero-fills the part of a box that lies past it); what TMA needs
     // is a 16-byte row pitch, which make_map_2d checks on lda and ldb.
-    int rc = make_map_2d(&core.map_a, a, 2, m, k, lda, BM, BK);
+    core.a_mn = (flags & FU_GEMM_A_KM) ? 1 : 0;
+    core.b_mn = (flags & FU_GEMM_B_KN) ? 1 : 0;
+    int rc = core.a_mn ? make_map_2d(&core.map_a, a, 2, k, m, lda, 64, 64) : make_map_2d(&core.map_a, a, 2, m, k, lda, BM, BK);
     if (rc != FU_OK) {
         return rc;
     }
-    rc = make_map_2d(&core.map_b, b, 2, n, k, ldb, BN, BK);
+    rc = core.b_mn ? make_map_2d(&core.map_b, b, 2, k, n, ldb, 64, 64) : make_map_2d(&core.map_b, b, 2, n, k, ldb, BN, BK);
     if (rc != FU_OK) {
         return rc;
     }
@@ -501,7 +503,7 @@ extern "C" int fu_gemm_bf16(const FuGemmArgs* g, void* stream)
         return fu::fail(FU_E_ARG, "fu_gemm_bf16: C (and the residual) need 16-byte aligned rows");
     }
     PlainArgs a{};
-    int       rc = fill_core(a.core, g->a, g->b, g->m, g->n, g->k, g->lda, g->ldb, g->err);
+    int       rc = fill_core(a.core, g->a, g->b, g->m, g->n, g->k, g->lda, g->ldb, g->err, g->flags);
     if (rc != FU_OK) {
         return rc;
     }

@@ -1,6 +1,8 @@
 #pragma once
 // A persistent, warp-specialised bf16 GEMM for sm_100a: D[M,N] = A[M,K] * B[N,K]^T with fp32
-// accumulation in tensor memory.
+// accumulation in tensor memory. Either operand may instead be given with the contraction along
+// its rows (A stored K x M, B stored K x N, "MN-major"): the weight gradient of a linear layer
+// contracts over the tokens and reads dY and X as they lie in memory, without a transposed copy.
 //
 //   warp 0      TMA producer: A and B tiles (128B-swizzled, K-major) into a 4-stage shared-memory ring
 //   warp 1      MMA issuer:   one elected thread issues tcgen05.mma 128x256x16, accumulators in TMEM
@@ -49,6 +51,7 @@ struct Core {
     CUtensorMap map_b;
     int         M, N, K;
     int         tiles_m, tiles_n;
+    int         a_mn, b_mn;  // operand stored K x M (K x N): tiles are fetched as 64 x 64 blocks
     uint32_t*   err;
 };
 
@@ -139,8 +142,22 @@ __device__ __forceinline__ void run(const Core& core, Epi& epi, Src src = Src{},
                     uint8_t* sa = ring + s * STAGE_BYTES;
                     uint8_t* sb = sa + A_BYTES;
                     ptx::mbar_expect_tx(&full[s], STAGE_BYTES);
-                    ptx::tma_load_2d(sa, &core.map_a, kb * BK, mt * BM, &full[s]);
-                    ptx::tma_load_2d(sb, &core.map_b, kb * BK, nt * BN, &full[s]);
+                    if (!core.a_mn) {
+                        ptx::tma_load_2d(sa, &core.map_a, kb * BK, mt * BM, &full[s]);
+                    }
+                    else {  // 64 (k) x 64 (m) blocks of 8 KiB, one per 64 columns of the tile
+                        for (int j = 0; j < BM / 64; ++j) {
+                            ptx::tma_load_2d(sa + j * 8192, &core.map_a, mt * BM + j * 64, kb * BK, &full[s]);
+                        }
+                    }
+                    if (!core.b_mn) {
+                        ptx::tma_load_2d(sb, &core.map_b, kb * BK, nt * BN, &full[s]);
+                    }
+                    else {
+                        for (int j = 0; j < BN / 64; ++j) {
+                            ptx::tma_load_2d(sb + j * 8192, &core.map_b, nt * BN + j * 64, kb * BK, &full[s]);
+                        }
+                    }
                 }
             }
         }
@@ -148,8 +165,12 @@ __device__ __forceinline__ void run(const Core& core, Epi& epi, Src src = Src{},
     }
     else if (warp == 1) {
         if (lane == 0) {
-            constexpr uint32_t idesc = ptx::make_idesc(1, 1, BM, BN, 0, 0);
-            uint32_t           it    = 0;
+            const uint32_t idesc = ptx::make_idesc(1, 1, BM, BN, core.a_mn ? 1 : 0, core.b_mn ? 1 : 0);
+            // K-major: 16 bf16 along K are 32 bytes inside the swizzle atom (+2 in the descriptor's
+            // 16-byte units). MN-major: 16 rows of K are 2048 bytes (+128), 64-column blocks 8 KiB apart.
+            const uint32_t a_lbo = core.a_mn ? 8192u : 16u, a_step = core.a_mn ? 128u : 2u;
+            const uint32_t b_lbo = core.b_mn ? 8192u : 16u, b_step = core.b_mn ? 128u : 2u;
+            uint32_t       it    = 0;
             uint32_t           tcount = 0;
             bool               ok    = true;
             for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tcount) {
@@ -170,13 +191,11 @@ __device__ __forceinline__ void run(const Core& core, Epi& epi, Src src = Src{},
                     }
                     ptx::tc_fence_after();
                     const uint32_t sa     = base + s * STAGE_BYTES;
-                    const uint64_t a_desc = ptx::smem_desc_sw128(sa, 16, 1024);
-                    const uint64_t b_desc = ptx::smem_desc_sw128(sa + A_BYTES, 16, 1024);
+                    const uint64_t a_desc = ptx::smem_desc_sw128(sa, a_lbo, 1024);
+                    const uint64_t b_desc = ptx::smem_desc_sw128(sa + A_BYTES, b_lbo, 1024);
 #pragma unroll
                     for (int k = 0; k < BK / UMMA_K; ++k) {
-                        // 16 bf16 = 32 bytes further along K inside the swizzle atom: +2 in the
-                        // descriptor's 16-byte address units
-                        ptx::mma_f16_ss(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc, (kb | k) != 0);
+                        ptx::mma_f16_ss(d_tmem, a_desc + a_step * k, b_desc + b_step * k, idesc, (kb | k) != 0);
                     }
                     ptx::mma_commit(&empty[s]);
                 }

@@ -16,6 +16,14 @@ using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t
 
 inline EncodeTiledFn encode_tiled_fn()
 {
+    // The encoder is a driver call and wants a current context on the calling thread. A thread that
+    // has made no runtime call yet (an autograd worker whose first CUDA work is one of these
+    // launches) has none: a no-op runtime call binds the device's primary context to it.
+    static thread_local bool bound = false;
+    if (!bound) {
+        cudaFree(nullptr);
+        bound = true;
+    }
     static EncodeTiledFn fn = nullptr;
     if (!fn) {
         void*                           p = nullptr;

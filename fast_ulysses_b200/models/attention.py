@@ -84,9 +84,9 @@ class _SPAttention(torch.autograd.Function):
         dy2 = dy.reshape(m, hidden)
         if not dy2.is_contiguous():
             dy2 = dy2.contiguous()
-        db_o = dy2.float().sum(0).to(dy.dtype) if ctx.has_bias else None
+        db_o = dy2.sum(0, dtype=torch.float32).to(dy.dtype) if ctx.has_bias else None
         # dW_o[n, k] = sum_m dy[m, n] A[m, k]
-        dw_o = gemm.gemm_bf16(gemm.transpose_for_gemm(dy2), gemm.transpose_for_gemm(gather))
+        dw_o = gemm.gemm_bf16(dy2, gather, a_km=True, b_kn=True)
         # dA = dy W_o, scattered to the head owners from the GEMM epilogue (mode-0 direction)
         mod._launch_scatter(dy2, w_o.t().contiguous(), mod.do_win, 1, 0, None, None, None)
         dqkv = torch.empty(3, b, mod.s_total, mod.n_local, HEAD_DIM, dtype=torch.bfloat16, device=dy.device)
@@ -102,8 +102,8 @@ class _SPAttention(torch.autograd.Function):
         qkv.qk_norm_rope_bwd(back[0], back[1], y_save, dyqkv, mod.rope, gamma_q, gamma_k, dgq, dgk, heads=N,
                              s_local=s_local, eps=mod.eps)
         dyqkv[:, 2 * N * HEAD_DIM:].copy_(back[2])
-        dx = gemm.gemm_bf16(dyqkv, gemm.transpose_for_gemm(w_qkv)).view(b, s_local, hidden)
-        dw_qkv = gemm.gemm_bf16(gemm.transpose_for_gemm(dyqkv), gemm.transpose_for_gemm(x2))
+        dx = gemm.gemm_bf16(dyqkv, w_qkv, b_kn=True).view(b, s_local, hidden)
+        dw_qkv = gemm.gemm_bf16(dyqkv, x2, a_km=True, b_kn=True)
         return dx, dw_qkv, dgq.to(gamma_q.dtype), dgk.to(gamma_k.dtype), dw_o, db_o, None
 
 

@@ -73,7 +73,8 @@ def route_from_row(row) -> FuRoute:
 class FuGemmArgs(C.Structure):
     _fields_ = [("a", C.c_void_p), ("b", C.c_void_p), ("c", C.c_void_p), ("m", C.c_int64), ("n", C.c_int64),
                 ("k", C.c_int64), ("lda", C.c_int64), ("ldb", C.c_int64), ("ldc", C.c_int64), ("bias", C.c_void_p),
-                ("residual", C.c_void_p), ("act", C.c_int32), ("ctas", C.c_int32), ("err", C.c_void_p)]
+                ("residual", C.c_void_p), ("act", C.c_int32), ("ctas", C.c_int32), ("err", C.c_void_p),
+                ("flags", C.c_int32)]
 
 
 class FuQkvArgs(C.Structure):

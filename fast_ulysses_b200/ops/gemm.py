@@ -52,13 +52,18 @@ def transpose_for_gemm(x: torch.Tensor) -> torch.Tensor:
 
 def gemm_bf16(a: torch.Tensor, b: torch.Tensor, *, bias: torch.Tensor | None = None,
               residual: torch.Tensor | None = None, act: int = 0, out: torch.Tensor | None = None,
-              ctas: int = 0) -> torch.Tensor:
-    """``out[m, n] = act(a[m, :] . b[n, :] + bias[n]) + residual[m, n]`` (bf16 in, bf16 out)."""
+              ctas: int = 0, a_km: bool = False, b_kn: bool = False) -> torch.Tensor:
+    """``out[m, n] = act(a[m, :] . b[n, :] + bias[n]) + residual[m, n]`` (bf16 in, bf16 out).
+
+    ``a_km`` / ``b_kn``: that operand is given with the contraction along its rows, ``a`` as
+    ``(k, m)`` and ``b`` as ``(k, n)``; the kernel reads it as it lies in memory (no transposed
+    copy), which is what the weight gradient ``dY^T X`` of a linear layer wants."""
     assert a.is_cuda and b.is_cuda and a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
-    assert a.dim() == 2 and b.dim() == 2 and a.shape[1] == b.shape[1], (a.shape, b.shape)
+    assert a.dim() == 2 and b.dim() == 2
     a, b = _tma_ready(a), _tma_ready(b)
-    m, k = a.shape
-    n = b.shape[0]
+    k, m = (a.shape[0], a.shape[1]) if a_km else (a.shape[1], a.shape[0])
+    kb, n = (b.shape[0], b.shape[1]) if b_kn else (b.shape[1], b.shape[0])
+    assert k == kb, (a.shape, b.shape, a_km, b_kn)
     if out is None:
         out = torch.empty(m, n, dtype=torch.bfloat16, device=a.device)
     assert out.shape == (m, n) and out.stride(1) == 1 and out.dtype == torch.bfloat16
@@ -74,6 +79,7 @@ def gemm_bf16(a: torch.Tensor, b: torch.Tensor, *, bias: torch.Tensor | None = N
         g.residual = residual.data_ptr()
     g.act = act
     g.ctas = ctas
+    g.flags = (1 if a_km else 0) | (2 if b_kn else 0)
     g.err = error_word(a.device).data_ptr()
     lib = ck.lib()
     ck.check(lib.fu_gemm_bf16(C.byref(g), ck.stream_ptr()))
@@ -96,13 +102,13 @@ class _Linear(torch.autograd.Function):
         gy2 = gy.reshape(-1, gy.shape[-1]).contiguous()
         gx = gw = gb = None
         if ctx.needs_input_grad[0]:
-            # dX[m, k] = sum_n dY[m, n] W[n, k]  ->  A = dY (m x n), B = W^T (k x n)
-            gx = gemm_bf16(gy2, transpose_for_gemm(weight)).view(ctx.x_shape)
+            # dX[m, k] = sum_n dY[m, n] W[n, k]: W as stored is the (contraction x output) operand
+            gx = gemm_bf16(gy2, weight, b_kn=True).view(ctx.x_shape)
         if ctx.needs_input_grad[1]:
-            # dW[n, k] = sum_m dY[m, n] X[m, k]  ->  A = dY^T (n x m), B = X^T (k x m)
-            gw = gemm_bf16(transpose_for_gemm(gy2), transpose_for_gemm(x2))
+            # dW[n, k] = sum_m dY[m, n] X[m, k]: both operands contract along their rows
+            gw = gemm_bf16(gy2, x2, a_km=True, b_kn=True)
         if ctx.has_bias and ctx.needs_input_grad[2]:
-            gb = gy2.float().sum(0).to(gy.dtype)
+            gb = gy2.sum(0, dtype=torch.float32).to(gy.dtype)
         return gx, gw, gb
 
 

@@ -87,3 +87,17 @@ def test_linear_autograd_with_a_token_count_that_is_not_a_multiple_of_8(tokens):
     torch.nn.functional.linear(xr, wr, br).backward(gy.float())
     assert rel_err(y, torch.nn.functional.linear(xr, wr, br)) < 1e-2
     assert rel_err(x.grad, xr.grad) < 1e-2 and rel_err(w.grad, wr.grad) < 1e-2 and rel_err(b.grad, br.grad) < 1e-2
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (300, 520, 200), (5120, 384, 9450), (72, 40, 1001)])
+@pytest.mark.parametrize("a_km,b_kn", [(True, True), (False, True), (True, False)])
+def test_operands_given_with_the_contraction_along_their_rows(m, n, k, a_km, b_kn):
+    torch.manual_seed(m + n + k)
+    a = (torch.randn(m, k, device="cuda") * 0.5).bfloat16()
+    b = (torch.randn(n, k, device="cuda") * 0.5).bfloat16()
+    want = a.float() @ b.float().t()
+    if (a_km and m % 8) or (b_kn and n % 8):
+        pytest.skip("a row pitch of the stored operand must be a multiple of 16 bytes")
+    got = gemm.gemm_bf16(a.t().contiguous() if a_km else a, b.t().contiguous() if b_kn else b, a_km=a_km, b_kn=b_kn)
+    gemm.check_errors()
+    assert rel_err(got, want) < 5e-3
