@@ -339,15 +339,18 @@ __global__ void __launch_bounds__(THREADS, 1) fmha_fwd_kernel(const __grid_const
                 }
                 const float mc = m_ref * c;
                 // P = exp2(S * c - m_ref * c), written over S as packed bf16
-                float l4[4] = {0.f, 0.f, 0.f, 0.f};
+                const float nmc = -mc;
+                float       l4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
                 for (int ch = 0; ch < 4; ++ch) {
                     uint32_t pk[16];
 #pragma unroll
                     for (int i = 0; i < 16; ++i) {
-                        const float e0 = ptx::ex2(fmaf(__uint_as_float(r[ch * 32 + 2 * i]), c, -mc));
-                        const float e1 = ptx::ex2(fmaf(__uint_as_float(r[ch * 32 + 2 * i + 1]), c, -mc));
-                        l4[i & 3] += e0 + e1;
+                        float x0, x1;
+                        ptx::fma2(x0, x1, __uint_as_float(r[ch * 32 + 2 * i]), __uint_as_float(r[ch * 32 + 2 * i + 1]), c, c,
+                                  nmc, nmc);
+                        const float e0 = ptx::ex2(x0), e1 = ptx::ex2(x1);
+                        ptx::add2(l4[(2 * i) & 3], l4[(2 * i + 1) & 3], l4[(2 * i) & 3], l4[(2 * i + 1) & 3], e0, e1);
                         pk[i] = ptx::pack_bf16x2(e0, e1);
                     }
                     ptx::tmem_st_32x16(ts + ch * 16, pk);
