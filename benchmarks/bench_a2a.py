@@ -130,9 +130,11 @@ def main():
         from fast_ulysses_b200.ops import fp8
 
         x128 = torch.randn(1, s_local, heads, 128, device="cuda", dtype=torch.bfloat16)
+        x8 = torch.randint(-128, 127, (1, s_local, heads, 128), device="cuda", dtype=torch.int8)
+        # the block-scaled time includes the quantise and dequantise kernels around the exchange
         emit(rank, mode="fp8", world=world, bf16_ms=run(lambda: g.all_to_all_4d(x128), args.iters),
              fp8_block_scaled_ms=run(lambda: fp8.all_to_all_4d_fp8(g, x128), args.iters),
-             int8_ms=run(lambda: g.all_to_all_4d(x128.view(torch.int8)[..., :128].contiguous()), args.iters))
+             int8_payload_ms=run(lambda: g.all_to_all_4d(x8), args.iters))
     g.check()
     g.destroy()
     dist.destroy_process_group()
