@@ -90,10 +90,10 @@ __global__ void __launch_bounds__(THREADS, 1) fmha_bwd_dkdv_kernel(const __grid_
         }
         for (int g = 0; g < 2; ++g) {
             ptx::mbar_init(&bar.sd_full[g], 1);
-            ptx::mbar_init(&bar.p_ready[g], 256);
+            ptx::mbar_init(&bar.p_ready[g], 8);
         }
         ptx::mbar_init(&bar.acc_full, 1);
-        ptx::mbar_init(&bar.acc_free, 256);
+        ptx::mbar_init(&bar.acc_free, 8);
         ptx::mbar_fence_init();
         ptx::tma_prefetch_desc(&p.map_q);
         ptx::tma_prefetch_desc(&p.map_do);
@@ -165,15 +165,15 @@ __global__ void __launch_bounds__(THREADS, 1) fmha_bwd_dkdv_kernel(const __grid_
                 for (int kk = 0; kk < D / 16; ++kk) {  // S^T = K Q^T
                     const uint32_t a_off = (kk >> 2) * HALF_BYTES + (kk & 3) * 32;
                     const uint32_t b_off = (kk >> 2) * Q_HALF + (kk & 3) * 32;
-                    ptx::mma_f16_ss(tmem + g * 128, ptx::smem_desc_sw128(sk_addr + a_off, 16, 1024),
-                                    ptx::smem_desc_sw128(qa + b_off, 16, 1024), idesc_sd, kk != 0);
+                    ptx::mma_f16_ss(tmem + g * 128, ptx::desc_advance(ptx::smem_desc_sw128(sk_addr, 16, 1024), a_off),
+                                    ptx::desc_advance(ptx::smem_desc_sw128(qa, 16, 1024), b_off), idesc_sd, kk != 0);
                 }
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {  // dP^T = V dO^T
                     const uint32_t a_off = (kk >> 2) * HALF_BYTES + (kk & 3) * 32;
                     const uint32_t b_off = (kk >> 2) * Q_HALF + (kk & 3) * 32;
-                    ptx::mma_f16_ss(tmem + g * 128 + 64, ptx::smem_desc_sw128(sv_addr + a_off, 16, 1024),
-                                    ptx::smem_desc_sw128(oa + b_off, 16, 1024), idesc_sd, kk != 0);
+                    ptx::mma_f16_ss(tmem + g * 128 + 64, ptx::desc_advance(ptx::smem_desc_sw128(sv_addr, 16, 1024), a_off),
+                                    ptx::desc_advance(ptx::smem_desc_sw128(oa, 16, 1024), b_off), idesc_sd, kk != 0);
                 }
                 ptx::mma_commit(&bar.sd_full[g]);
             };
@@ -183,12 +183,12 @@ __global__ void __launch_bounds__(THREADS, 1) fmha_bwd_dkdv_kernel(const __grid_
 #pragma unroll
                 for (int kk = 0; kk < BQ / 16; ++kk) {  // dV += P^T dO   (contraction over the 64 query rows)
                     ptx::mma_f16_ts(tmem + 256, tmem + g * 128 + (kk >> 1) * 32 + (kk & 1) * 8,
-                                    ptx::smem_desc_sw128(oa + kk * 2048, Q_HALF, 1024), idesc_ac, accumulate || kk != 0);
+                                    ptx::desc_advance(ptx::smem_desc_sw128(oa, Q_HALF, 1024), kk * 2048), idesc_ac, accumulate || kk != 0);
                 }
 #pragma unroll
                 for (int kk = 0; kk < BQ / 16; ++kk) {  // dK += dS^T Q
                     ptx::mma_f16_ts(tmem + 384, tmem + g * 128 + 64 + (kk >> 1) * 32 + (kk & 1) * 8,
-                                    ptx::smem_desc_sw128(qa + kk * 2048, Q_HALF, 1024), idesc_ac, accumulate || kk != 0);
+                                    ptx::desc_advance(ptx::smem_desc_sw128(qa, Q_HALF, 1024), kk * 2048), idesc_ac, accumulate || kk != 0);
                 }
             };
 
@@ -289,7 +289,7 @@ __global__ void __launch_bounds__(THREADS, 1) fmha_bwd_dkdv_kernel(const __grid_
                 }
                 ptx::tmem_st_wait();
                 ptx::tc_fence_before();
-                ptx::mbar_arrive(&bar.p_ready[g]);
+                ptx::mbar_arrive_warp(&bar.p_ready[g]);
             }
             if (!ok) {
                 break;
@@ -325,7 +325,7 @@ __global__ void __launch_bounds__(THREADS, 1) fmha_bwd_dkdv_kernel(const __grid_
                 }
             }
             ptx::tc_fence_before();
-            ptx::mbar_arrive(&bar.acc_free);
+            ptx::mbar_arrive_warp(&bar.acc_free);
         }
     }
 

@@ -92,9 +92,9 @@ __global__ void __launch_bounds__(THREADS, 1) fmha_bwd_dq_kernel(const __grid_co
         }
         for (int t = 0; t < QT; ++t) {
             ptx::mbar_init(&bar.sd_full[t], 1);
-            ptx::mbar_init(&bar.ds_ready[t], 256);
+            ptx::mbar_init(&bar.ds_ready[t], 8);
             ptx::mbar_init(&bar.dq_final[t], 1);
-            ptx::mbar_init(&bar.dq_free[t], 256);
+            ptx::mbar_init(&bar.dq_free[t], 8);
         }
         ptx::mbar_fence_init();
         ptx::tma_prefetch_desc(&p.map_q);
@@ -170,15 +170,15 @@ __global__ void __launch_bounds__(THREADS, 1) fmha_bwd_dq_kernel(const __grid_co
                 for (int kk = 0; kk < D / 16; ++kk) {  // S = Q K^T
                     const uint32_t a_off = (kk >> 2) * HALF_BYTES + (kk & 3) * 32;
                     const uint32_t b_off = (kk >> 2) * KV_HALF + (kk & 3) * 32;
-                    ptx::mma_f16_ss(tmem + t * 256, ptx::smem_desc_sw128(qa + a_off, 16, 1024),
-                                    ptx::smem_desc_sw128(ka + b_off, 16, 1024), idesc_sd, kk != 0);
+                    ptx::mma_f16_ss(tmem + t * 256, ptx::desc_advance(ptx::smem_desc_sw128(qa, 16, 1024), a_off),
+                                    ptx::desc_advance(ptx::smem_desc_sw128(ka, 16, 1024), b_off), idesc_sd, kk != 0);
                 }
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {  // dP = dO V^T
                     const uint32_t a_off = (kk >> 2) * HALF_BYTES + (kk & 3) * 32;
                     const uint32_t b_off = (kk >> 2) * KV_HALF + (kk & 3) * 32;
-                    ptx::mma_f16_ss(tmem + t * 256 + 64, ptx::smem_desc_sw128(oa + a_off, 16, 1024),
-                                    ptx::smem_desc_sw128(va + b_off, 16, 1024), idesc_sd, kk != 0);
+                    ptx::mma_f16_ss(tmem + t * 256 + 64, ptx::desc_advance(ptx::smem_desc_sw128(oa, 16, 1024), a_off),
+                                    ptx::desc_advance(ptx::smem_desc_sw128(va, 16, 1024), b_off), idesc_sd, kk != 0);
                 }
                 ptx::mma_commit(&bar.sd_full[t]);
             };
@@ -189,7 +189,7 @@ __global__ void __launch_bounds__(THREADS, 1) fmha_bwd_dq_kernel(const __grid_co
                     // K step tile as an MN-major operand: 16 kv rows = 2048 bytes further down, the two
                     // 64-wide halves of d are KV_HALF apart, 8-row groups 1024 bytes apart
                     ptx::mma_f16_ts(tmem + t * 256 + 128, tmem + t * 256 + (kk >> 1) * 32 + (kk & 1) * 8,
-                                    ptx::smem_desc_sw128(ka + kk * 2048, KV_HALF, 1024), idesc_dq, accumulate || kk != 0);
+                                    ptx::desc_advance(ptx::smem_desc_sw128(ka, KV_HALF, 1024), kk * 2048), idesc_dq, accumulate || kk != 0);
                 }
             };
 
@@ -308,7 +308,7 @@ __global__ void __launch_bounds__(THREADS, 1) fmha_bwd_dq_kernel(const __grid_co
                 }
                 ptx::tmem_st_wait();
                 ptx::tc_fence_before();
-                ptx::mbar_arrive(&bar.ds_ready[t]);
+                ptx::mbar_arrive_warp(&bar.ds_ready[t]);
             }
             if (!ok) {
                 break;
@@ -339,7 +339,7 @@ __global__ void __launch_bounds__(THREADS, 1) fmha_bwd_dq_kernel(const __grid_co
                 }
             }
             ptx::tc_fence_before();
-            ptx::mbar_arrive(&bar.dq_free[t]);
+            ptx::mbar_arrive_warp(&bar.dq_free[t]);
         }
     }
 
