@@ -43,6 +43,7 @@ struct RouteX {
     int32_t        rows_per_chunk;
     int64_t        row_groups;      // ceil(rows / rows_per_chunk)
     int64_t        count;           // chunks in this route
+    int32_t        peer;            // rank whose choice of buffer shifts `dst` (-1: dst is final)
 };
 
 struct RouteSet {
@@ -58,6 +59,11 @@ struct KArgs {
     FuCtrl*  peer_ctrl[FU_MAX_WORLD];
     int      rank, world, flags;
     uint64_t timeout_ns;
+    // Output pool: `dst` of a route to rank p is built for p's window; if p announces pool buffer
+    // k for this call, the route is shifted by pool_delta[p][k - 1] = buffer - window.
+    int64_t  pool_delta[FU_MAX_WORLD][FU_POOL_SLOTS];
+    int32_t  n_pool, my_slot;
+    int8_t   peer_slot[FU_MAX_WORLD];
 };
 
 struct Chunk {
@@ -70,8 +76,12 @@ struct Chunk {
 // Round-robin over routes: virtual index v names (route v % n, chunk v / n); a route that has run
 // out of chunks yields nothing for that v. With gridDim a multiple of n each CTA streams to one peer.
 struct ChunkCursor {
-    int64_t v, stride, end;
-    __device__ ChunkCursor(const RouteSet& s, int cta, int ctas) : v(cta), stride(ctas), end(s.max_count * s.n) {}
+    int64_t        v, stride, end;
+    const int64_t* shift;  // per-rank destination shift (shared memory), or null
+    __device__ ChunkCursor(const RouteSet& s, int cta, int ctas, const int64_t* shift_ = nullptr)
+        : v(cta), stride(ctas), end(s.max_count * s.n), shift(shift_)
+    {
+    }
     __device__ bool next(const RouteSet& s, Chunk& c)
     {
         while (v < end) {
@@ -93,6 +103,9 @@ struct ChunkCursor {
             c.row_bytes = static_cast<uint32_t>(min(r.piece_bytes, r.row_bytes - col0));
             c.src       = r.src + batch * r.src_batch + row0 * r.src_pitch + col0;
             c.dst       = r.dst + batch * r.dst_batch + row0 * r.dst_pitch + col0;
+            if (shift && r.peer >= 0) {
+                c.dst += shift[r.peer];
+            }
             c.src_pitch = r.src_pitch;
             c.dst_pitch = r.dst_pitch;
             return true;
@@ -113,10 +126,15 @@ __device__ void report(FuCtrl* own, uint32_t code, uint32_t peer, uint64_t expec
 }
 
 // Called by one full warp. Lane p < world announces `value` to rank p.
-__device__ void announce(const KArgs& a, uint64_t value)
+__device__ void announce(const KArgs& a, uint64_t value, bool with_slot = false)
 {
     const int lane = threadIdx.x & 31;
     if (lane < a.world && !(a.flags & FU_A2A_MUTE)) {
+        if (with_slot) {
+            // where this rank wants the payload of this call; ordered before the announcement by
+            // the release below (same thread, same destination rank)
+            *reinterpret_cast<volatile uint8_t*>(&a.peer_ctrl[lane]->slot_of[a.rank]) = static_cast<uint8_t>(a.my_slot);
+        }
         red_release_sys_max(&a.peer_ctrl[lane]->flags[a.rank], value);
     }
 }
@@ -188,11 +206,12 @@ __device__ __forceinline__ void bulk_issue_stores(const BulkPipe& p, int s, cons
 
 // Moves this CTA's share of a route set with one warp. `jbase` continues the stage/parity sequence
 // across successive calls in one kernel. Returns false if a load never completed.
-__device__ bool bulk_move(const RouteSet& set, const BulkPipe& p, int64_t& jbase, FuCtrl* own)
+__device__ bool bulk_move(const RouteSet& set, const BulkPipe& p, int64_t& jbase, FuCtrl* own,
+                          const int64_t* shift = nullptr)
 {
     const int   lane = threadIdx.x & 31;
-    ChunkCursor load_cur(set, blockIdx.x, gridDim.x);
-    ChunkCursor store_cur(set, blockIdx.x, gridDim.x);
+    ChunkCursor load_cur(set, blockIdx.x, gridDim.x, shift);
+    ChunkCursor store_cur(set, blockIdx.x, gridDim.x, shift);
     Chunk       c;
     int64_t     jl = jbase;  // next chunk number to load
     int64_t     js = jbase;  // next chunk number to store
@@ -237,9 +256,9 @@ __device__ bool bulk_move(const RouteSet& set, const BulkPipe& p, int64_t& jbase
 // `kCoherent` selects plain loads: required when the source was written during this launch (the own
 // window, filled by peers), where the read-only path must not be used.
 template <bool kCoherent>
-__device__ void ldst_move(const RouteSet& set)
+__device__ void ldst_move(const RouteSet& set, const int64_t* shift = nullptr)
 {
-    ChunkCursor cur(set, blockIdx.x, gridDim.x);
+    ChunkCursor cur(set, blockIdx.x, gridDim.x, shift);
     Chunk       c;
     while (cur.next(set, c)) {
         const uint32_t vpr  = c.row_bytes >> 4;
@@ -275,6 +294,7 @@ __global__ void __launch_bounds__(kBulk ? 32 : kLdstThreads, kBulk ? 1 : kLdstCt
     extern __shared__ __align__(1024) uint8_t smem[];
     __shared__ uint64_t                       full_bar[kStages];
     __shared__ uint32_t                       ticket_s;
+    __shared__ int64_t                        shift_s[FU_MAX_WORLD];  // destination shift per rank (output pool)
 
     const int  warp      = threadIdx.x >> 5;
     const bool handshake = !(a.flags & FU_A2A_NO_HANDSHAKE);
@@ -309,12 +329,26 @@ __global__ void __launch_bounds__(kBulk ? 32 : kLdstThreads, kBulk ? 1 : kLdstCt
     bool alive = true;
     if (handshake && warp == 0) {
         if (blockIdx.x == 0) {
-            announce(a, base + 1);
+            announce(a, base + 1, true);
             if (a.flags & FU_A2A_EARLY_PUBLISH) {
                 announce(a, base + 2);
             }
         }
         alive = await(a, base + 1, FU_ST_OPEN_TIMEOUT);
+    }
+    if (warp == 0) {
+        // Which buffer each rank wants this call's payload in: announced with the opening flag
+        // (the acquire in await() orders this read), or given by the host when there is no handshake.
+        const int lane = threadIdx.x & 31;
+        if (lane < a.world) {
+            int slot = handshake ? static_cast<int>(*reinterpret_cast<volatile uint8_t*>(&own->slot_of[lane]))
+                                 : static_cast<int>(a.peer_slot[lane]);
+            if (slot < 0 || slot > a.n_pool) {
+                slot = 0;  // a rank that announced nothing usable is reported by the handshake itself
+            }
+            shift_s[lane] = slot > 0 ? a.pool_delta[lane][slot - 1] : 0;
+        }
+        __syncwarp();
     }
     if (stamps) {
         own->stamps[1] = globaltimer_ns();
@@ -323,12 +357,12 @@ __global__ void __launch_bounds__(kBulk ? 32 : kLdstThreads, kBulk ? 1 : kLdstCt
     int64_t chunk_no = 0;
     if (kBulk) {
         if (alive) {
-            alive = bulk_move(a.push, pipe, chunk_no, own);
+            alive = bulk_move(a.push, pipe, chunk_no, own, shift_s);
         }
     }
     else {
         __syncthreads();
-        ldst_move<false>(a.push);
+        ldst_move<false>(a.push, shift_s);
     }
     // Make this CTA's payload visible system-wide before its arrival can be observed.
     fence_sys();
@@ -461,6 +495,26 @@ extern "C" int fu_a2a4d(const FuA2AArgs* args, void* stream_v)
     if (in.n_routes > 0 && !aligned16(in.src)) {
         return fu::fail(FU_E_ARG, "fu_a2a4d: the input is not 16-byte aligned");
     }
+    if (in.n_pool < 0 || in.n_pool > FU_POOL_SLOTS || in.my_slot < 0 || in.my_slot > in.n_pool) {
+        return fu::fail(FU_E_ARG, "fu_a2a4d: pool buffer %d of %d", in.my_slot, in.n_pool);
+    }
+    k.n_pool  = in.n_pool;
+    k.my_slot = in.my_slot;
+    for (int p = 0; p < in.world; ++p) {
+        k.peer_slot[p] = in.peer_slot[p];
+        if ((in.flags & FU_A2A_NO_HANDSHAKE) && (in.peer_slot[p] < 0 || in.peer_slot[p] > in.n_pool)) {
+            return fu::fail(FU_E_ARG, "fu_a2a4d: rank %d is given pool buffer %d of %d", p, in.peer_slot[p], in.n_pool);
+        }
+        for (int s = 0; s < in.n_pool; ++s) {
+            if (!in.peer_pool[p][s] || !aligned16(in.peer_pool[p][s])) {
+                return fu::fail(FU_E_ARG, "fu_a2a4d: pool buffer %d of rank %d is missing or not 16-byte aligned", s, p);
+            }
+            k.pool_delta[p][s] = static_cast<const uint8_t*>(in.peer_pool[p][s]) - static_cast<const uint8_t*>(in.peer_win[p]);
+        }
+    }
+    if (in.my_slot > 0 && in.out != in.peer_pool[in.rank][in.my_slot - 1]) {
+        return fu::fail(FU_E_ARG, "fu_a2a4d: with pool buffer %d chosen, `out` must be that buffer", in.my_slot);
+    }
     const bool    ldst  = (in.flags & FU_A2A_LDST) != 0;
     const int64_t chunk = ldst ? kLdstChunkBytes : kStageBytes;
     const bool    copy_out = in.out && in.out_bytes > 0;
@@ -473,8 +527,9 @@ extern "C" int fu_a2a4d(const FuA2AArgs* args, void* stream_v)
     auto granular = [](const FuRoute& r) {
         return ((r.row_bytes | r.src_off | r.dst_off | r.src_pitch | r.dst_pitch | r.src_batch | r.dst_batch) & 15) == 0;
     };
-    auto expand = [&](const FuRoute& r, const uint8_t* src_base, uint8_t* dst_base) {
+    auto expand = [&](const FuRoute& r, const uint8_t* src_base, uint8_t* dst_base, int shift_peer = -1) {
         RouteX x{};
+        x.peer      = shift_peer;
         x.src       = src_base + r.src_off;
         x.dst       = dst_base + r.dst_off;
         x.src_pitch = r.src_pitch;
@@ -502,7 +557,8 @@ extern "C" int fu_a2a4d(const FuA2AArgs* args, void* stream_v)
         // The own share never needs the window when the caller wants the result elsewhere.
         const bool direct = copy_out && in.own_direct && r.peer == in.rank;
         uint8_t*   dst    = direct ? static_cast<uint8_t*>(in.out) : static_cast<uint8_t*>(in.peer_win[r.peer]);
-        RouteX     x      = expand(r, static_cast<const uint8_t*>(in.src), dst);
+        // a route into another rank's memory follows that rank's choice of buffer for this call
+        RouteX     x      = expand(r, static_cast<const uint8_t*>(in.src), dst, direct ? -1 : r.peer);
         if (x.count > 0) {
             k.push.r[k.push.n++] = x;
             k.push.max_count     = std::max(k.push.max_count, x.count);

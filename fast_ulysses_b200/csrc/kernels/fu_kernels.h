@@ -31,7 +31,9 @@ typedef struct FuCtrl {
     uint32_t arrive[2];            // CTA arrival counters used inside one launch
     uint32_t status[6];            // [0] code, [1] peer, [2,3] expected, [4,5] seen (FU_ST_*)
     uint64_t stamps[8];            // globaltimer ns: start, opened, pushed, closed, done
-    uint64_t pad_[11];
+    uint8_t  slot_of[FU_MAX_WORLD];  // written by rank p with its opening announcement: where rank p
+                                   // wants this call's payload (0 = its window, k = its pool buffer k)
+    uint64_t pad_[10];
 } FuCtrl;  // 256 bytes
 
 #define FU_CTRL_BYTES 256
@@ -63,6 +65,12 @@ enum {
                                 // an unordered stream: take a third of the device, not two thirds
 };
 
+// Output pool. A rank may ask its peers, per call, to write into one of up to FU_POOL_SLOTS extra
+// symmetric buffers instead of its window: the result is then already where the caller will read
+// it and nothing is copied out. Each rank chooses for itself (whichever of its buffers is free, or
+// none) and tells the others in the opening handshake, so ranks never have to agree.
+#define FU_POOL_SLOTS 4
+
 typedef struct FuA2AArgs {
     const void* src;                    // this rank's input
     void*       peer_win[FU_MAX_WORLD]; // window base on every rank (own entry included)
@@ -83,6 +91,14 @@ typedef struct FuA2AArgs {
     int32_t     own_direct;
     int32_t     n_out_routes;
     FuRoute     out_routes[2];
+    // Output pool (append-only fields): buffer k of every rank, how many there are, and this rank's
+    // choice for this call (0 = window; then `out`, if given, is filled by the fused copy-out as
+    // before; k > 0 = pool buffer k - 1, and `out` must be that buffer's local address).
+    // `peer_slot` replaces the exchanged choices when FU_A2A_NO_HANDSHAKE is set.
+    void*       peer_pool[FU_MAX_WORLD][FU_POOL_SLOTS];
+    int32_t     n_pool;
+    int32_t     my_slot;
+    int8_t      peer_slot[FU_MAX_WORLD];
 } FuA2AArgs;
 
 FU_API int fu_a2a4d(const FuA2AArgs* args, void* stream);

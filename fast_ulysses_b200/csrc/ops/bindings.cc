@@ -64,6 +64,7 @@ struct Prepared {
     at::Tensor  output;
     Window*     window        = nullptr;
     bool        out_is_window = false;
+    int         pool_slot     = 0;  // > 0: `output` is that buffer of the output pool
 };
 
 // The kernel reads a view in place when only the batch and sequence strides are irregular.
@@ -139,6 +140,15 @@ Prepared prepare(Group& g, const at::Tensor& input, int64_t mode, const Splits& 
         }
         else {
             p.window = &g.window(role, window_bytes);
+            if (!p.output.defined() && role == Role::kSync && g.output_pool()) {
+                // The result is born in a pooled symmetric buffer that the peers write directly
+                // (this rank tells them which one in the opening handshake). When every buffer is
+                // still referenced by a live tensor, this rank alone falls back to window + copy-out.
+                p.pool_slot = g.take_pool_slot(window_bytes);
+                if (p.pool_slot > 0) {
+                    p.output = g.pool_output(p.pool_slot, p.plan->out_shape, dtype);
+                }
+            }
             if (!p.output.defined()) {
                 p.output = at::empty(p.plan->out_shape, p.x.options().memory_format(at::MemoryFormat::Contiguous));
             }
@@ -168,7 +178,7 @@ void run_prepared(Group& g, Prepared& p, cudaStream_t stream, int extra_flags)
     }
     const int64_t out_bytes = nbytes_of(p.plan->out_shape, p.x.scalar_type());
     g.launch(*p.plan, p.x.data_ptr(), *p.window, p.out_is_window ? nullptr : p.output.data_ptr(),
-             p.out_is_window ? 0 : out_bytes, stream, extra_flags);
+             p.out_is_window ? 0 : out_bytes, stream, extra_flags, p.pool_slot);
 }
 
 cudaStream_t current_stream(const Group& g)
@@ -484,6 +494,9 @@ TORCH_LIBRARY(fast_ulysses_b200, m)
         .def("set_timeout_ms", &fu::Group::set_timeout_ms)
         .def("set_ctas", &fu::Group::set_ctas)
         .def("windows_allocated", &fu::Group::windows_allocated)
+        .def("set_output_pool", [](const c10::intrusive_ptr<fu::Group>& g, bool on) { g->set_output_pool(on); })
+        .def("output_pool", [](const c10::intrusive_ptr<fu::Group>& g) { return g->output_pool(); })
+        .def("pool_hits", [](const c10::intrusive_ptr<fu::Group>& g) { return g->pool_hits(); })
         .def("symm_alloc", &fu::Group::symm_alloc)
         .def("symm_ptrs", &fu::Group::symm_ptrs)
         .def("barrier",

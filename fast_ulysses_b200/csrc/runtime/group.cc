@@ -1,5 +1,7 @@
 #include "group.hpp"
 
+#include <cstdlib>
+
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
 #include <cuda_runtime.h>
@@ -105,6 +107,9 @@ Group::Group(std::string group_name, int64_t rank, int64_t world, int64_t device
     TORCH_CHECK(world >= 1 && world <= FU_MAX_WORLD, "world_size must be in [1, ", FU_MAX_WORLD,
                 "]: the exchange runs inside one NVLink domain, got ", world);
     TORCH_CHECK(rank >= 0 && rank < world, "rank ", rank, " is outside a group of ", world);
+    if (const char* e = std::getenv("FU_OUTPUT_POOL")) {
+        pool_enabled_ = std::string(e) != "0";  // must be the same on every rank
+    }
 }
 
 Group::~Group()
@@ -262,6 +267,49 @@ Window& Group::lend_window(int64_t bytes)
     return slot;
 }
 
+int Group::take_pool_slot(int64_t bytes)
+{
+    check_alive();
+    if (pool_.empty() || pool_capacity_ < bytes) {
+        // Collective: `bytes` is the window size of the plan, which every rank computes alike, so
+        // all ranks arrive here in the same call. Buffers of the old pool that tensors still refer
+        // to stay alive through those tensors.
+        pool_.clear();
+        for (int k = 0; k < kPoolSlots; ++k) {
+            PoolSlot s;
+            s.w    = std::make_shared<Window>(allocate(bytes));
+            s.busy = std::make_shared<std::atomic<int>>(0);
+            pool_.push_back(std::move(s));
+        }
+        pool_capacity_ = pool_[0].w->capacity;
+    }
+    for (size_t k = 0; k < pool_.size(); ++k) {
+        int expected = 0;
+        if (pool_[k].busy->compare_exchange_strong(expected, 1)) {
+            ++pool_hits_;
+            return static_cast<int>(k) + 1;
+        }
+    }
+    return 0;
+}
+
+at::Tensor Group::pool_output(int slot, at::IntArrayRef shape, at::ScalarType dtype)
+{
+    TORCH_CHECK(slot >= 1 && slot <= static_cast<int>(pool_.size()), "pool buffer ", slot, " does not exist");
+    const PoolSlot& s      = pool_[static_cast<size_t>(slot - 1)];
+    const int64_t   nbytes = c10::multiply_integers(shape) * static_cast<int64_t>(c10::elementSize(dtype));
+    TORCH_CHECK(nbytes <= s.w->capacity, "pool buffer of ", s.w->capacity, " bytes cannot hold ", nbytes);
+    // The tensor owns the buffer's "in use" mark and a reference to the allocation: the buffer goes
+    // back to the pool when the last reference to the tensor's storage is dropped, and the memory
+    // stays mapped even if the pool itself has been replaced or the group destroyed by then.
+    std::shared_ptr<Window>           keep = s.w;
+    std::shared_ptr<std::atomic<int>> busy = s.busy;
+    const c10::Device dev(c10::DeviceType::CUDA, static_cast<c10::DeviceIndex>(device_index_));
+    return at::from_blob(
+        s.w->base[static_cast<size_t>(rank_)], shape, [keep, busy](void*) { busy->store(0); },
+        at::TensorOptions().dtype(dtype).device(dev));
+}
+
 at::Tensor Group::view_of(const Window& w, at::IntArrayRef shape, at::ScalarType dtype)
 {
     const int64_t nbytes = c10::multiply_integers(shape) * static_cast<int64_t>(c10::elementSize(dtype));
@@ -322,10 +370,18 @@ void Group::prune_owned()
 }
 
 void Group::launch(const Plan& plan, const void* src, const Window& w, void* out, int64_t out_bytes, void* stream,
-                   int extra_flags)
+                   int extra_flags, int pool_slot)
 {
     FuA2AArgs a{};
     a.src = src;
+    // Every rank passes the whole pool, whatever it chose itself: a peer may have chosen any buffer.
+    a.n_pool  = static_cast<int32_t>(pool_.size());
+    a.my_slot = pool_slot;
+    for (size_t k = 0; k < pool_.size(); ++k) {
+        for (int p = 0; p < world_; ++p) {
+            a.peer_pool[p][k] = pool_[k].w->base[static_cast<size_t>(p)];
+        }
+    }
     for (int p = 0; p < world_; ++p) {
         a.peer_win[p]  = w.base[p];
         a.peer_ctrl[p] = w.ctrl[p];
@@ -364,7 +420,8 @@ void Group::launch(const Plan& plan, const void* src, const Window& w, void* out
         // Own share straight into the caller's tensor; only what peers wrote is copied out.
         a.own_direct   = 1;
         a.n_out_routes = 0;
-        for (const Route& r : plan.from_peers) {
+        // With a pool buffer chosen the peers write `out` themselves: nothing is copied out.
+        for (const Route& r : (pool_slot > 0 ? std::vector<Route>{} : plan.from_peers)) {
             FuRoute& o  = a.out_routes[a.n_out_routes++];
             o.peer      = rank_;
             o.src_off   = r.src_off;
@@ -540,6 +597,8 @@ void Group::destroy()
     }
     plans_.clear();
     windows_.clear();
+    pool_.clear();
+    pool_capacity_ = 0;
     for (auto& w : lent_) {
         w = Window{};
     }

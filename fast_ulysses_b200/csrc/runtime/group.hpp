@@ -14,6 +14,7 @@
 #include <torch/custom_class.h>
 
 #include <array>
+#include <atomic>
 #include <map>
 #include <memory>
 #include <optional>
@@ -41,6 +42,14 @@ struct Window {
 };
 
 constexpr int     kLentSlots     = 4;
+constexpr int     kPoolSlots     = 3;  // <= FU_POOL_SLOTS
+
+// One buffer of the output pool: a symmetric allocation (shared with the tensors handed out of it,
+// so it outlives the pool if it must) and whether a tensor handed out of it is still alive.
+struct PoolSlot {
+    std::shared_ptr<Window>           w;
+    std::shared_ptr<std::atomic<int>> busy;
+};
 constexpr size_t  kPlanCacheCap  = 512;
 
 class Group : public torch::CustomClassHolder {
@@ -61,6 +70,15 @@ public:
 
     Window&       window(Role role, int64_t bytes);
     Window&       lend_window(int64_t bytes);
+    // Output pool of the copying call. `take_pool_slot` is COLLECTIVE when the pool has to be
+    // created or grown (every rank calls it with the same `bytes` at the same point) and otherwise
+    // a local decision: the index + 1 of a buffer no live tensor refers to, or 0 when there is
+    // none (the call then goes through the window and is copied out, on this rank only).
+    int           take_pool_slot(int64_t bytes);
+    at::Tensor    pool_output(int slot, at::IntArrayRef shape, at::ScalarType dtype);
+    bool          output_pool() const { return pool_enabled_; }
+    void          set_output_pool(bool on) { pool_enabled_ = on; }
+    int64_t       pool_hits() const { return pool_hits_; }
     at::Tensor    make_output(at::IntArrayRef shape, at::ScalarType dtype, int64_t window_bytes);
     const Window* window_of(const at::Tensor& t) const;
     // A caller-owned symmetric byte buffer for the fused operators (q/k/v windows, attention
@@ -75,7 +93,7 @@ public:
 
     // Launch on `stream`. `out` may be null (result stays in the window).
     void launch(const Plan& plan, const void* src, const Window& w, void* out, int64_t out_bytes, void* stream,
-                int extra_flags);
+                int extra_flags, int pool_slot = 0);
     void barrier(Role role, void* stream);
 
     // CPU/gloo execution of the same plan.
@@ -112,6 +130,10 @@ private:
     std::array<Window, kLentSlots>       lent_;
     uint64_t                             lend_calls_ = 0;
     std::map<void*, Window>              owned_;    // empty_output() buffers by data pointer
+    std::vector<PoolSlot>                pool_;
+    int64_t                              pool_capacity_ = 0;
+    bool                                 pool_enabled_  = true;
+    int64_t                              pool_hits_     = 0;
 };
 
 }  // namespace fu

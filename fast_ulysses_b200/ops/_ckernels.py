@@ -11,6 +11,7 @@ import ctypes as C
 from pathlib import Path
 
 FU_MAX_WORLD = 8
+FU_POOL_SLOTS = 4
 FU_CTRL_BYTES = 256
 
 FU_A2A_NO_HANDSHAKE = 1
@@ -32,7 +33,9 @@ class FuA2AArgs(C.Structure):
                 ("peer_ctrl", C.c_void_p * FU_MAX_WORLD), ("out", C.c_void_p), ("out_bytes", C.c_int64),
                 ("rank", C.c_int32), ("world", C.c_int32), ("n_routes", C.c_int32), ("flags", C.c_int32),
                 ("ctas", C.c_int32), ("timeout_ms", C.c_uint32), ("routes", FuRoute * FU_MAX_WORLD),
-                ("own_direct", C.c_int32), ("n_out_routes", C.c_int32), ("out_routes", FuRoute * 2)]
+                ("own_direct", C.c_int32), ("n_out_routes", C.c_int32), ("out_routes", FuRoute * 2),
+                ("peer_pool", (C.c_void_p * FU_POOL_SLOTS) * FU_MAX_WORLD), ("n_pool", C.c_int32),
+                ("my_slot", C.c_int32), ("peer_slot", C.c_int8 * FU_MAX_WORLD)]
 
 
 _lib = None

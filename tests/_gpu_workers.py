@@ -153,6 +153,66 @@ def correctness(rank, world):
     assert failed.item() == 0
 
 
+def output_pool(rank, world):
+    """The copying call hands out pooled symmetric buffers that the peers write directly. Ranks hold
+    different numbers of results alive, so they choose different buffers (or none) for the same call."""
+    dev = torch.device("cuda", rank)
+    g = UlyssesGroup(device=dev)
+    h = g._handle
+    fails = []
+
+    def expect(cond, what):
+        if not cond:
+            fails.append(what)
+
+    def call(seed, mode=0):
+        torch.manual_seed(seed * 131 + rank)
+        shape = (2, 160, 2 * world, 128) if mode == 0 else (2, 160 * world, 2, 128)
+        x = torch.randn(shape, device=dev, dtype=torch.bfloat16)
+        return g.all_to_all_4d(x, mode=mode), ref_even(x, mode, world)
+
+    expect(h.output_pool(), "pool is on by default")
+    held, wants = [], []
+    for step in range(6):
+        # rank r keeps its first r results alive (at most three): rank 0 always takes the first
+        # buffer, the last ranks run out of buffers and fall back to their window
+        y, want = call(step, mode=step % 2)
+        expect(torch.equal(y, want), f"step {step}")
+        if len(held) < min(rank, 3):
+            held.append(y)
+            wants.append(want)
+        for i, (t, w) in enumerate(zip(held, wants)):
+            expect(torch.equal(t, w), f"held result {i} after step {step}")
+    hits = h.pool_hits()
+    # the result of the previous step is still referenced while the next call runs, so a rank that
+    # holds two results finds no free buffer every other step, and one that holds three never again
+    expect(hits == {0: 6, 1: 6, 2: 4}.get(rank, 3), f"pool hits {hits} on rank {rank}")
+    # the zero-copy and the lent paths next to it
+    torch.manual_seed(7 + rank)
+    x = torch.randn(2, 160, 2 * world, 128, device=dev, dtype=torch.bfloat16)
+    out = g.empty_output(x)
+    g.all_to_all_4d(x, out=out)
+    expect(torch.equal(out, ref_even(x, 0, world)), "out=")
+    expect(torch.equal(g.all_to_all_4d_async(x, lend=True).wait(), ref_even(x, 0, world)), "lend")
+    # a larger call replaces the pool on every rank together; older results stay valid
+    torch.manual_seed(11 + rank)
+    xb = torch.randn(2, 400, 2 * world, 128, device=dev, dtype=torch.bfloat16)
+    expect(torch.equal(g.all_to_all_4d(xb), ref_even(xb, 0, world)), "grown pool")
+    for i, (t, w) in enumerate(zip(held, wants)):
+        expect(torch.equal(t, w), f"held result {i} after growth")
+    # switched off (on every rank): window + copy-out again
+    h.set_output_pool(False)
+    y, want = call(99)
+    expect(torch.equal(y, want) and h.pool_hits() == hits + 1, "pool off")
+    g.barrier()
+    g.check()
+    failed = torch.tensor([len(fails)], device=dev)
+    dist.all_reduce(failed)
+    g.destroy()
+    assert not fails, fails
+    assert failed.item() == 0
+
+
 def validation_uniform(rank, world):
     """Rejections raise on every rank before the first handshake: the barrier after each case
     would otherwise wait for a rank that went ahead."""

@@ -169,6 +169,88 @@ def test_group_single_rank_paths():
         g.all_to_all_4d(x)
 
 
+@pytest.mark.parametrize("flags", [0, ck.FU_A2A_LDST], ids=["bulk", "ldst"])
+@pytest.mark.parametrize("mode", [0, 1])
+def test_pool_buffers_chosen_rank_by_rank(flags, mode):
+    """Emulated ranks, each with its own choice of destination: its window, or one of two pool buffers.
+    Every sender must follow every receiver's choice."""
+    b, d, dtype = 2, 64, torch.bfloat16
+    seq, heads = [40, 33, 0, 52, 17], [2, 3, 1, 2, 2]
+    ws = len(seq)
+    slots = [1, 0, 2, 2, 1]
+    glob = global_tensor(b, sum(seq), sum(heads), d, dtype)
+    inputs, expected = shards(glob, seq, heads, mode)
+    elem = glob.element_size()
+    plans = [plan_debug(b, d, r, ws, seq, heads, mode, elem) for r in range(ws)]
+    wbytes = (plans[0][1] * elem + 255) // 256 * 256
+    wins = [torch.zeros(wbytes + ck.FU_CTRL_BYTES, dtype=torch.uint8, device="cuda") for _ in range(ws)]
+    pools = [[torch.zeros(wbytes, dtype=torch.uint8, device="cuda") for _ in range(2)] for _ in range(ws)]
+    stream = torch.cuda.current_stream().cuda_stream
+    for r in range(ws):
+        a = ck.FuA2AArgs()
+        a.src = inputs[r].data_ptr()
+        for p in range(ws):
+            a.peer_win[p] = wins[p].data_ptr()
+            a.peer_ctrl[p] = wins[p].data_ptr() + wbytes
+            a.peer_slot[p] = slots[p]
+            for k in range(2):
+                a.peer_pool[p][k] = pools[p][k].data_ptr()
+        a.n_pool, a.my_slot = 2, slots[r]
+        a.rank, a.world = r, ws
+        a.flags = flags | ck.FU_A2A_NO_HANDSHAKE
+        rows = plans[r][2].tolist()
+        a.n_routes = len(rows)
+        for i, row in enumerate(rows):
+            a.routes[i] = ck.route_from_row(row)
+        if slots[r] > 0:  # the own share goes straight into the chosen buffer, nothing is copied out
+            a.out = pools[r][slots[r] - 1].data_ptr()
+            a.out_bytes = expected[r].numel() * elem
+            a.own_direct = 1
+        ck.check(ck.lib().fu_a2a4d(C.byref(a), C.c_void_p(stream)))
+    torch.cuda.synchronize()
+    for r in range(ws):
+        n = expected[r].numel() * elem
+        where = wins[r] if slots[r] == 0 else pools[r][slots[r] - 1]
+        assert torch.equal(where[:n], expected[r].contiguous().view(torch.uint8).reshape(-1)), f"rank {r}"
+        for k in range(2):
+            if k != slots[r] - 1:
+                assert not pools[r][k].any(), f"rank {r}: buffer {k} was not chosen but was written"
+    # a choice that does not exist is refused on the host
+    a.my_slot = 3
+    assert ck.lib().fu_a2a4d(C.byref(a), C.c_void_p(stream)) != 0
+
+
+def test_output_pool_of_the_copying_call():
+    g = fu.UlyssesGroup(device="cuda")
+    h = g._handle
+    assert h.output_pool()
+    x = torch.randn(2, 300, 8, 128, device="cuda", dtype=torch.bfloat16)
+    held = [g.all_to_all_4d(x) for _ in range(3)]
+    assert h.pool_hits() == 3 and len({t.data_ptr() for t in held}) == 3
+    n_alloc = h.windows_allocated()
+    extra = g.all_to_all_4d(x)  # every buffer is referenced: this call goes through the window
+    assert h.pool_hits() == 3 and torch.equal(extra, x) and extra.data_ptr() not in {t.data_ptr() for t in held}
+    first = held[0].data_ptr()
+    view = held[0][:, :10]  # a view keeps the buffer alive
+    del held[0]
+    y = g.all_to_all_4d(x)
+    assert h.pool_hits() == 3 and torch.equal(view, x[:, :10])
+    del view, y
+    y = g.all_to_all_4d(x)
+    assert h.pool_hits() == 4 and y.data_ptr() == first and h.windows_allocated() == n_alloc
+    assert all(torch.equal(t, x) for t in held)
+    # a larger call replaces the pool; results handed out before stay valid
+    big = torch.randn(2, 700, 8, 128, device="cuda", dtype=torch.bfloat16)
+    yb = g.all_to_all_4d(big)
+    assert torch.equal(yb, big) and h.windows_allocated() > n_alloc and all(torch.equal(t, x) for t in held)
+    h.set_output_pool(False)
+    hits = h.pool_hits()
+    assert torch.equal(g.all_to_all_4d(x), x) and h.pool_hits() == hits
+    g.check()
+    g.destroy()
+    assert torch.equal(y, x) and torch.equal(yb, big)  # the memory outlives the group
+
+
 def test_cuda_graph_replay_advances_epoch():
     g = fu.UlyssesGroup(device="cuda")
     x = torch.randn(1, 512, 8, 128, device="cuda", dtype=torch.bfloat16)

@@ -55,6 +55,11 @@ def test_sync_async_coexist(world):
     run_ranks(world, "_gpu_workers", "sync_async_coexist", backend="nccl", timeout=300)
 
 
+@pytest.mark.parametrize("world", world_sizes())
+def test_output_pool(world):
+    run_ranks(world, "_gpu_workers", "output_pool", backend="nccl", timeout=300)
+
+
 @pytest.mark.parametrize("world", world_sizes()[:1])
 def test_window_reuse_race(world):
     run_ranks(world, "_gpu_workers", "window_reuse_race", backend="nccl", timeout=300)
