@@ -243,6 +243,13 @@ class UlyssesGroup:
         """Synchronises, then raises if any device-side handshake of this group ran out of time."""
         self._handle.check()
 
+    def set_output_pool(self, enabled: bool) -> None:
+        """Whether ``all_to_all_4d(x)`` returns a pooled symmetric buffer that the peers write
+        directly (default, no copy-out) or a fresh tensor filled by a copy out of the window.
+        Call it with the same value on every rank, between collectives."""
+        if self.device.type != "cpu":
+            self._handle.set_output_pool(bool(enabled))
+
     def destroy(self) -> None:
         """Release the group's windows. Collective. Buffers from ``empty_output()`` are yours."""
         if self._destroyed:
