@@ -287,7 +287,10 @@ def main() -> int:
             "config": {"model": "Wan2.1-14B 720p attention exchange", "global_batch": 1, "seq_len": TOTAL_TOKENS,
                        "heads": HEADS, "head_dim": HEAD_DIM, "per_rank_shape": [1, s_local, HEADS, HEAD_DIM],
                        "parallelism": f"sp{world}", "l2": "flushed between steps (256 MiB write)",
-                       "bytes_per_rank": x.numel() * 2},
+                       "bytes_per_rank": x.numel() * 2,
+                       "copying_call": ("result returned in a pooled symmetric buffer written by the peers "
+                                        "(library default; FU_OUTPUT_POOL=0 gives window + copy-out)")
+                       if args.impl == "ours" else "the reference's copying call"},
             "clocks": clocks,
             "e2e": {"value": e2e_ms, "unit": "ms", "h2d_bytes_per_step": x.numel() * 2, "d2h_bytes_per_step": 2048},
             # one fused a2a4d kernel per timed step of the headline metric; the attention block in
