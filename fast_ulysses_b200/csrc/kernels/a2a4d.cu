@@ -295,6 +295,7 @@ __global__ void __launch_bounds__(kBulk ? 32 : kLdstThreads, kBulk ? 1 : kLdstCt
     __shared__ uint64_t                       full_bar[kStages];
     __shared__ uint32_t                       ticket_s;
     __shared__ int64_t                        shift_s[FU_MAX_WORLD];  // destination shift per rank (output pool)
+    __shared__ int                            alive_s;                // did the opening handshake complete
 
     const int  warp      = threadIdx.x >> 5;
     const bool handshake = !(a.flags & FU_A2A_NO_HANDSHAKE);
@@ -348,6 +349,9 @@ __global__ void __launch_bounds__(kBulk ? 32 : kLdstThreads, kBulk ? 1 : kLdstCt
             }
             shift_s[lane] = slot > 0 ? a.pool_delta[lane][slot - 1] : 0;
         }
+        if (lane == 0) {
+            alive_s = alive ? 1 : 0;
+        }
         __syncwarp();
     }
     if (stamps) {
@@ -362,7 +366,11 @@ __global__ void __launch_bounds__(kBulk ? 32 : kLdstThreads, kBulk ? 1 : kLdstCt
     }
     else {
         __syncthreads();
-        ldst_move<false>(a.push, shift_s);
+        // Nothing is pushed after an opening handshake that ran out of time: a rank that never
+        // announced has not said where it wants its payload either.
+        if (alive_s) {
+            ldst_move<false>(a.push, shift_s);
+        }
     }
     // Make this CTA's payload visible system-wide before its arrival can be observed.
     fence_sys();
