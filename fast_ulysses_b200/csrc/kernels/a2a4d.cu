@@ -10,6 +10,11 @@
 // at once. Ordering rests on the PTX memory model only: payload copies complete, fence.acq_rel.sys,
 // CTA arrival counter, then red.release.sys on the peer's flag; the reader spins with
 // ld.acquire.sys. Every spin is bounded and reports through the control block's status words.
+//
+// Where a rank's payload lands is that rank's choice per call: its window, or one of its pooled
+// output buffers (then nothing is copied out afterwards). The choice travels with the opening
+// announcement (FuCtrl::slot_of) and every sender shifts its routes to that rank accordingly, so
+// ranks with different numbers of live results need not agree on anything.
 #include "fu_kernels.h"
 #include "host_util.h"
 #include "ptx.cuh"
