@@ -289,7 +289,7 @@ def main() -> int:
                        "parallelism": f"sp{world}", "l2": "flushed between steps (256 MiB write)",
                        "bytes_per_rank": x.numel() * 2,
                        "copying_call": ("result returned in a pooled symmetric buffer written by the peers "
-                                        "(library default; FU_OUTPUT_POOL=0 gives window + copy-out)")
+                                        "(library default; group.set_output_pool(False) gives window + copy-out)")
                        if args.impl == "ours" else "the reference's copying call"},
             "clocks": clocks,
             "e2e": {"value": e2e_ms, "unit": "ms", "h2d_bytes_per_step": x.numel() * 2, "d2h_bytes_per_step": 2048},

@@ -1,7 +1,5 @@
 #include "group.hpp"
 
-#include <cstdlib>
-
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
 #include <cuda_runtime.h>
@@ -107,9 +105,6 @@ Group::Group(std::string group_name, int64_t rank, int64_t world, int64_t device
     TORCH_CHECK(world >= 1 && world <= FU_MAX_WORLD, "world_size must be in [1, ", FU_MAX_WORLD,
                 "]: the exchange runs inside one NVLink domain, got ", world);
     TORCH_CHECK(rank >= 0 && rank < world, "rank ", rank, " is outside a group of ", world);
-    if (const char* e = std::getenv("FU_OUTPUT_POOL")) {
-        pool_enabled_ = std::string(e) != "0";  // must be the same on every rank
-    }
 }
 
 Group::~Group()
