@@ -140,7 +140,14 @@ Prepared prepare(Group& g, const at::Tensor& input, int64_t mode, const Splits& 
         }
         else {
             p.window = &g.window(role, window_bytes);
-            if (!p.output.defined() && role == Role::kSync && g.output_pool()) {
+            // Not while a CUDA graph is being captured: a replay keeps writing the buffer chosen at
+            // capture time, whoever holds it by then, so a captured call takes the window and a
+            // tensor from the graph's own memory pool instead.
+            cudaStreamCaptureStatus capture = cudaStreamCaptureStatusNone;
+            cudaStreamIsCapturing(at::cuda::getCurrentCUDAStream(static_cast<c10::DeviceIndex>(g.device_index())),
+                                  &capture);
+            if (!p.output.defined() && role == Role::kSync && g.output_pool()
+                && capture == cudaStreamCaptureStatusNone) {
                 // The result is born in a pooled symmetric buffer that the peers write directly
                 // (this rank tells them which one in the opening handshake). When every buffer is
                 // still referenced by a live tensor, this rank alone falls back to window + copy-out.

@@ -268,6 +268,21 @@ def test_cuda_graph_replay_advances_epoch():
         assert torch.all(out == float(i))
     # capture does not execute; five replays, two phases each
     assert g._handle.epoch_debug(out, 2) == e0 + 10
+    # the copying call inside a capture: the result must not come out of the output pool, whose
+    # buffers go back to other callers while the graph is still replayed
+    y0 = g.all_to_all_4d(x)  # warm: window and pool exist
+    hits = g._handle.pool_hits()
+    torch.cuda.synchronize()
+    graph2 = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph2):
+        y = g.all_to_all_4d(x)
+    assert g._handle.pool_hits() == hits
+    for i in range(3):
+        x.fill_(float(10 + i))
+        graph2.replay()
+        torch.cuda.synchronize()
+        assert torch.all(y == float(10 + i))
+    del y0
     g.destroy()
 
 
