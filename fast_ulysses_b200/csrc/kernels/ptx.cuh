@@ -375,21 +375,6 @@ __device__ __forceinline__ float ex2(float x)
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
-// 2^x on the FMA/ALU pipes instead of the special-function unit: floor by a round-down add of
-// 1.5 * 2^23, a cubic for 2^f on [0, 1) (max relative error about 1e-4, far below bf16's 4e-3), and
-// the integer part added into the exponent field. The SFU retires only 16 ex2 per clock per SM,
-// which is as long as the MMAs of an attention tile take, so kernels split their exponentials
-// between the two pipes. Valid for x >= -126 (callers clamp).
-__device__ __forceinline__ float ex2_poly(float x)
-{
-    float t;
-    asm("add.rm.ftz.f32 %0, %1, %2;" : "=f"(t) : "f"(x), "f"(12582912.0f));
-    const float f = x - (t - 12582912.0f);
-    float       p = fmaf(0.077119089663029f, f, 0.227564394474030f);
-    p             = fmaf(p, f, 0.695146143436432f);
-    p             = fmaf(p, f, 1.0f);
-    return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
-}
 __device__ __forceinline__ float lg2(float x)
 {
     float y;
