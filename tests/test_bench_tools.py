@@ -1,0 +1,53 @@
+"""The benchmark helpers that only read the GPUs' state: run against a fake nvidia-smi on PATH."""
+
+import os
+import stat
+import subprocess
+import sys
+import textwrap
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def fake_smi(tmp_path, foreign_pids):
+    """An `nvidia-smi` that answers the two queries exclusive.py makes."""
+    path = tmp_path / "nvidia-smi"
+    apps = "\n".join(f"{pid}, GPU-0000" for pid in foreign_pids)
+    path.write_text(textwrap.dedent(f"""\
+        #!/bin/sh
+        case "$*" in
+          *query-compute-apps*) printf '%s\\n' "{apps}" ;;
+          *query-gpu=clocks.sm*) echo 1755 ;;
+          *) echo fake ;;
+        esac
+        """))
+    path.chmod(path.stat().st_mode | stat.S_IEXEC)
+    return {**os.environ, "PATH": f"{tmp_path}:{os.environ['PATH']}"}
+
+
+def run_exclusive(env, *cmd):
+    return subprocess.run([sys.executable, os.path.join(ROOT, "benchmarks", "exclusive.py"), "--gpus", "0",
+                           "--sample-secs", "0.05", "--", *cmd], env=env, capture_output=True, text=True, timeout=60)
+
+
+def test_exclusive_run_reports_exclusive_and_the_minimum_clock(tmp_path):
+    r = run_exclusive(fake_smi(tmp_path, []), sys.executable, "-c", "import time; time.sleep(0.3)")
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "EXCLUSIVE" in r.stdout and "1755 MHz" in r.stdout
+
+
+def test_exclusive_refuses_to_start_beside_foreign_processes(tmp_path):
+    r = run_exclusive(fake_smi(tmp_path, [4242]), sys.executable, "-c", "print('must not run')")
+    assert r.returncode == 3 and "CONTENDED before start" in r.stdout and "must not run" not in r.stdout
+
+
+def test_exclusive_passes_the_command_exit_code_on(tmp_path):
+    r = run_exclusive(fake_smi(tmp_path, []), sys.executable, "-c", "import sys; sys.exit(7)")
+    assert r.returncode == 7
+
+
+def test_collect_and_bench_a2a_parse_their_arguments():
+    for script, arg in (("collect.py", "--help"), ("bench_a2a.py", "--help")):
+        r = subprocess.run([sys.executable, os.path.join(ROOT, "benchmarks", script), arg], capture_output=True,
+                           text=True, timeout=120)
+        assert r.returncode == 0 and "usage" in r.stdout.lower(), r.stderr[-500:]
