@@ -2,7 +2,7 @@
 L2 so that DRAM counters mean something, a few hundred MB on the device, one to three launches of
 the kernel of interest after a short warm-up.
 
-    python -m fast_ulysses_b200.utils.profile_cases a2a|gemm|qkv|outproj|fmha_fwd|fmha_bwd
+    python -m fast_ulysses_b200.utils.profile_cases a2a|gemm|qkv|outproj|fmha_fwd|fmha_bwd|fmha_bwd_det
 
 Each case prints the CUDA-event time of its last launch, so the same command is also a quick
 timing check when run without a profiler.
@@ -126,8 +126,18 @@ def case_fmha_bwd():
     print(f"fmha bwd S=16384 H=5: {ms:.4f} ms, {10 * 16384 ** 2 * 128 * 5 / ms / 1e9:.0f} TFLOP/s")
 
 
+def case_fmha_bwd_det():
+    from fast_ulysses_b200.ops import attention
+
+    q, k, v = _qkv_attn()
+    o, lse = attention.fmha_fwd(q, k, v)
+    d_o = torch.randn_like(o)
+    ms = _time(lambda: attention.fmha_bwd(q, k, v, o, lse, d_o, deterministic=True))
+    print(f"fmha bwd (two passes, no atomics) S=16384 H=5: {ms:.4f} ms, {10 * 16384 ** 2 * 128 * 5 / ms / 1e9:.0f} TFLOP/s")
+
+
 CASES = {"a2a": case_a2a, "gemm": case_gemm, "qkv": case_qkv, "outproj": case_outproj, "fmha_fwd": case_fmha_fwd,
-         "fmha_bwd": case_fmha_bwd}
+         "fmha_bwd": case_fmha_bwd, "fmha_bwd_det": case_fmha_bwd_det}
 
 if __name__ == "__main__":
     name = sys.argv[1] if len(sys.argv) > 1 else ""
