@@ -144,14 +144,14 @@ Prepared prepare(Group& g, const at::Tensor& input, int64_t mode, const Splits& 
             // capture time, whoever holds it by then, so a captured call takes the window and a
             // tensor from the graph's own memory pool instead.
             cudaStreamCaptureStatus capture = cudaStreamCaptureStatusNone;
-            cudaStreamIsCapturing(at::cuda::getCurrentCUDAStream(static_cast<c10::DeviceIndex>(g.device_index())),
-                                  &capture);
+            const cudaStream_t      cur = at::cuda::getCurrentCUDAStream(static_cast<c10::DeviceIndex>(g.device_index()));
+            cudaStreamIsCapturing(cur, &capture);
             if (!p.output.defined() && role == Role::kSync && g.output_pool()
                 && capture == cudaStreamCaptureStatusNone) {
                 // The result is born in a pooled symmetric buffer that the peers write directly
                 // (this rank tells them which one in the opening handshake). When every buffer is
                 // still referenced by a live tensor, this rank alone falls back to window + copy-out.
-                p.pool_slot = g.take_pool_slot(window_bytes);
+                p.pool_slot = g.take_pool_slot(window_bytes, cur);
                 if (p.pool_slot > 0) {
                     p.output = g.pool_output(p.pool_slot, p.plan->out_shape, dtype);
                 }

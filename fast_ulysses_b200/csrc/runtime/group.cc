@@ -262,7 +262,7 @@ Window& Group::lend_window(int64_t bytes)
     return slot;
 }
 
-int Group::take_pool_slot(int64_t bytes)
+int Group::take_pool_slot(int64_t bytes, void* stream)
 {
     check_alive();
     if (pool_.empty() || pool_capacity_ < bytes) {
@@ -281,6 +281,20 @@ int Group::take_pool_slot(int64_t bytes)
     for (size_t k = 0; k < pool_.size(); ++k) {
         int expected = 0;
         if (pool_[k].busy->compare_exchange_strong(expected, 1)) {
+            PoolSlot& s = pool_[k];
+            if (s.used && s.last_stream != stream) {
+                // Readers of the previous result were queued on the stream that produced it (a
+                // reader on a third stream is the caller's to order, as with any allocator).
+                // Everything queued there so far must finish before the peers may write again.
+                const c10::cuda::CUDAGuard guard(static_cast<c10::DeviceIndex>(device_index_));
+                cudaEvent_t ev = nullptr;
+                cuda_ok(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming), "cudaEventCreateWithFlags");
+                cuda_ok(cudaEventRecord(ev, static_cast<cudaStream_t>(s.last_stream)), "cudaEventRecord");
+                cuda_ok(cudaStreamWaitEvent(static_cast<cudaStream_t>(stream), ev, 0), "cudaStreamWaitEvent");
+                cuda_ok(cudaEventDestroy(ev), "cudaEventDestroy");
+            }
+            s.last_stream = stream;
+            s.used        = true;
             ++pool_hits_;
             return static_cast<int>(k) + 1;
         }

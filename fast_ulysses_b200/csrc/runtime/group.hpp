@@ -49,6 +49,11 @@ constexpr int     kPoolSlots     = 3;  // <= FU_POOL_SLOTS
 struct PoolSlot {
     std::shared_ptr<Window>           w;
     std::shared_ptr<std::atomic<int>> busy;
+    // The stream of the call that last filled this buffer. A tensor is dropped on the host while
+    // its readers may still be queued on that stream; a later call on the same stream is ordered
+    // after them, a call on another stream first waits for that stream (see take_pool_slot).
+    void* last_stream = nullptr;
+    bool  used        = false;
 };
 constexpr size_t  kPlanCacheCap  = 512;
 
@@ -74,7 +79,7 @@ public:
     // created or grown (every rank calls it with the same `bytes` at the same point) and otherwise
     // a local decision: the index + 1 of a buffer no live tensor refers to, or 0 when there is
     // none (the call then goes through the window and is copied out, on this rank only).
-    int           take_pool_slot(int64_t bytes);
+    int           take_pool_slot(int64_t bytes, void* stream);
     at::Tensor    pool_output(int slot, at::IntArrayRef shape, at::ScalarType dtype);
     bool          output_pool() const { return pool_enabled_; }
     void          set_output_pool(bool on) { pool_enabled_ = on; }

@@ -243,6 +243,21 @@ def test_output_pool_of_the_copying_call():
     big = torch.randn(2, 700, 8, 128, device="cuda", dtype=torch.bfloat16)
     yb = g.all_to_all_4d(big)
     assert torch.equal(yb, big) and h.windows_allocated() > n_alloc and all(torch.equal(t, x) for t in held)
+    # a buffer filled on one stream and taken again on another: the second call waits for what
+    # was queued on the first (here a slow reader of the dropped result)
+    side = torch.cuda.Stream()
+    tmp = g.all_to_all_4d(x)
+    acc = torch.zeros_like(tmp, dtype=torch.float32)
+    for _ in range(50):
+        acc += tmp.float()
+    del tmp
+    side.wait_stream(torch.cuda.current_stream())
+    other = torch.randn_like(x)
+    with torch.cuda.stream(side):
+        outs = [g.all_to_all_4d(other) for _ in range(4)]
+    torch.cuda.synchronize()
+    assert torch.allclose(acc, 50 * x.float()) and all(torch.equal(t, other) for t in outs)
+    del outs
     h.set_output_pool(False)
     hits = h.pool_hits()
     assert torch.equal(g.all_to_all_4d(x), x) and h.pool_hits() == hits
