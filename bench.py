@@ -11,7 +11,12 @@ Config (the one the baseline names): 81 frames -> 21x45x80 = 75600 tokens in tot
 over the N ranks, 40 heads, d = 128, bf16, b = 1, mode 0 (scatter heads, gather sequence) through
 the public copying call. Total work is fixed as N grows (strong scaling). Timing: CUDA events
 around every step, L2 flushed between steps by writing a 256 MiB buffer, a barrier and a device
-synchronise on both sides of the timed region, the maximum over ranks reported.
+synchronise on both sides of the timed region. The reported value is the median over the timed
+steps of each rank, maximum over ranks (the reference's own method: benchmark/bench_a2a.py:101-123
+takes medians after a warm-up); mean, minimum, maximum, the slowest step and the rank that owned it
+are printed beside it so that an outlier shows. The warm-up runs the requested number of steps and
+then keeps going until at least 30 ms of device time of the step itself have passed, the same rule
+in both arms, and the clock sampler has delivered its first row before any of that starts.
 """
 
 from __future__ import annotations
@@ -41,7 +46,7 @@ class ClockSampler:
               "clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index: int):
-        self.index, self.rows, self.proc = index, [], None
+        self.index, self.rows, self.proc, self.first = index, [], None, 0
 
     def start(self):
         try:
@@ -51,10 +56,20 @@ class ClockSampler:
             threading.Thread(target=self._pump, daemon=True).start()
         except OSError:
             self.proc = None
+            return
+        # nvidia-smi attaches to every GPU of the box while it starts; let that finish before
+        # anything is timed, so that its start-up never runs beside a timed step
+        t_end = time.time() + 20.0
+        while not self.rows and time.time() < t_end and self.proc.poll() is None:
+            time.sleep(0.05)
 
     def _pump(self):
         for line in self.proc.stdout:
             self.rows.append([c.strip() for c in line.split(",")])
+
+    def mark(self):
+        """Rows from here on belong to the timed region."""
+        self.first = len(self.rows)
 
     def stop(self) -> dict:
         if self.proc is None:
@@ -67,7 +82,7 @@ class ClockSampler:
             self.proc.kill()
         sm, mx, reasons = [], [], set()
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-        for r in self.rows:
+        for r in self.rows[self.first:] or self.rows[-1:]:
             if len(r) < 7:
                 continue
             try:
@@ -109,22 +124,57 @@ def sync_all(world: int):
     torch.cuda.synchronize()
 
 
-def time_steps(step, steps: int, warmup: int, world: int, flush: torch.Tensor) -> float:
-    """ms per step, device-timed per step with an L2 flush in between, max over ranks."""
-    for _ in range(warmup):
-        flush.zero_()
-        step()
-    sync_all(world)
-    starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
-    ends = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
-    for i in range(steps):
+MIN_WARM_MS = 30.0  # device time of the step itself that the warm-up must cover, in both arms
+
+
+def gather_rows(vals, world: int):
+    """Every rank's list of floats, as a list of lists indexed by rank (the same on every rank)."""
+    if world == 1:
+        return [list(vals)]
+    mine = torch.tensor(vals, device="cuda", dtype=torch.float64)
+    rows = [torch.empty_like(mine) for _ in range(world)]
+    dist.all_gather(rows, mine)
+    return [r.tolist() for r in rows]
+
+
+def run_timed(step, n: int, flush: torch.Tensor):
+    """Per-step device times (ms) of n steps, each preceded by an L2 flush outside its event pair."""
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(n)]
+    ends = [torch.cuda.Event(enable_timing=True) for _ in range(n)]
+    for i in range(n):
         flush.zero_()
         starts[i].record()
         step()
         ends[i].record()
+    torch.cuda.synchronize()
+    return [s.elapsed_time(e) for s, e in zip(starts, ends)]
+
+
+def time_steps_stats(step, steps: int, warmup: int, world: int, flush: torch.Tensor) -> dict:
+    """Device time per step. `ms` is the median over the timed steps of a rank, maximum over ranks."""
+    warm = run_timed(step, warmup, flush)
+    # keep warming until MIN_WARM_MS of the step's own device time have passed; every rank derives the
+    # same number of extra steps from the same gathered figures, so collectives stay matched
+    per_step = max(statistics.median(r) for r in gather_rows(warm, world))
+    done = per_step * warmup
+    extra_warm = 0 if done >= MIN_WARM_MS else min(2000, int((MIN_WARM_MS - done) / max(per_step, 1e-3)) + 1)
+    for _ in range(extra_warm):
+        flush.zero_()
+        step()
     sync_all(world)
-    total = sum(s.elapsed_time(e) for s, e in zip(starts, ends))
-    return max_over_ranks(total / steps, world)
+    rows = gather_rows(run_timed(step, steps, flush), world)
+    sync_all(world)
+    medians = [statistics.median(r) for r in rows]
+    worst_rank = max(range(world), key=lambda r: max(rows[r]))
+    worst_step = max(range(steps), key=lambda i: rows[worst_rank][i])
+    return {"ms": max(medians), "mean_ms": max(sum(r) / len(r) for r in rows), "min_ms": min(min(r) for r in rows),
+            "max_ms": rows[worst_rank][worst_step], "slowest_step": worst_step, "slowest_rank": worst_rank,
+            "median_by_rank": [round(m, 5) for m in medians], "warmup_steps_run": warmup + extra_warm}
+
+
+def time_steps(step, steps: int, warmup: int, world: int, flush: torch.Tensor) -> float:
+    """ms per step: median over steps, maximum over ranks (see time_steps_stats)."""
+    return time_steps_stats(step, steps, warmup, world, flush)["ms"]
 
 
 def make_group(impl: str, local: int, world: int):
@@ -232,8 +282,11 @@ def main() -> int:
 
     sampler = ClockSampler(local)
     if rank == 0:
-        sampler.start()
-    ms = time_steps(step, args.steps, warmup, world, flush)
+        sampler.start()  # returns once the first row has arrived
+    sync_all(world)
+    sampler.mark()
+    head = time_steps_stats(step, args.steps, warmup, world, flush)
+    ms = head["ms"]
     clocks = sampler.stop() if rank == 0 else {}
 
     # end to end: the step's input arrives from pinned host memory, its result is read back
@@ -246,15 +299,19 @@ def main() -> int:
         y = group.all_to_all_4d(x_dev, mode=0)
         probe_host.copy_(y.view(-1)[:1024], non_blocking=True)
 
-    e2e_ms = time_steps(e2e_step, max(3, args.steps // 5), warmup, world, flush)
+    e2e = time_steps_stats(e2e_step, max(5, args.steps // 2), warmup, world, flush)
+    e2e_ms = e2e["ms"]
 
-    extra = {}
+    extra = {"headline_steps": head, "e2e_steps": e2e}
+    if clocks.get("sm_mhz"):
+        extra["headline_ms_x_sm_mhz"] = ms * clocks["sm_mhz"]
     if not args.no_extras:
         y = step()
-        extra["mode1_ms"] = time_steps(lambda: group.all_to_all_4d(y, mode=1), args.steps, warmup, world, flush)
+        m1 = time_steps_stats(lambda: group.all_to_all_4d(y, mode=1), args.steps, warmup, world, flush)
         out = group.empty_output(x, mode=0)
-        extra["mode0_zero_copy_ms"] = time_steps(lambda: group.all_to_all_4d(x, mode=0, out=out), args.steps, warmup,
-                                                 world, flush)
+        zc = time_steps_stats(lambda: group.all_to_all_4d(x, mode=0, out=out), args.steps, warmup, world, flush)
+        extra["mode1_ms"], extra["mode1_steps"] = m1["ms"], m1
+        extra["mode0_zero_copy_ms"], extra["mode0_zero_copy_steps"] = zc["ms"], zc
         del out, y
         if world in PUBLISHED_MS:
             # the shape the reference publishes: q, k, v packed (d = 384) with a 227-token text tail
@@ -287,10 +344,10 @@ def main() -> int:
             "config": {"model": "Wan2.1-14B 720p attention exchange", "global_batch": 1, "seq_len": TOTAL_TOKENS,
                        "heads": HEADS, "head_dim": HEAD_DIM, "per_rank_shape": [1, s_local, HEADS, HEAD_DIM],
                        "parallelism": f"sp{world}", "l2": "flushed between steps (256 MiB write)",
-                       "bytes_per_rank": x.numel() * 2,
-                       "copying_call": ("result returned in a pooled symmetric buffer written by the peers "
-                                        "(library default; group.set_output_pool(False) gives window + copy-out)")
-                       if args.impl == "ours" else "the reference's copying call"},
+                       "bytes_per_rank": x.numel() * 2, "statistic": "median over steps, max over ranks"},
+            "copying_call": ("result returned in a pooled symmetric buffer written by the peers (library default; "
+                             "group.set_output_pool(False) gives window + copy-out)")
+            if args.impl == "ours" else "the reference's copying call",
             "clocks": clocks,
             "e2e": {"value": e2e_ms, "unit": "ms", "h2d_bytes_per_step": x.numel() * 2, "d2h_bytes_per_step": 2048},
             # one fused a2a4d kernel per timed step of the headline metric; the attention block in
