@@ -55,6 +55,11 @@ struct RouteSet {
     int     n;
     int64_t max_count;
     RouteX  r[FU_MAX_WORLD];
+    // When `pinned`, CTAs [first[g], first[g + 1]) serve route g and nothing else; the host sizes the
+    // ranges by what each route costs (bytes, and a local copy is several times cheaper per byte
+    // than one that crosses NVLink), so all routes end at about the same time.
+    int32_t pinned;
+    int16_t first[FU_MAX_WORLD + 1];
 };
 
 struct KArgs {
@@ -80,18 +85,37 @@ struct Chunk {
 
 // Round-robin over routes: virtual index v names (route v % n, chunk v / n); a route that has run
 // out of chunks yields nothing for that v. With gridDim a multiple of n each CTA streams to one peer.
+// The route a CTA is pinned to, or -1 when the set deals its chunks round-robin.
+__device__ __forceinline__ int pinned_route(const RouteSet& s, int cta)
+{
+    if (!s.pinned) {
+        return -1;
+    }
+    int g = 0;
+    while (g + 1 < s.n && cta >= s.first[g + 1]) {
+        ++g;
+    }
+    return g;
+}
+
 struct ChunkCursor {
     int64_t        v, stride, end;
+    int            route;  // >= 0: this CTA walks that route only (v is then a chunk index)
     const int64_t* shift;  // per-rank destination shift (shared memory), or null
     __device__ ChunkCursor(const RouteSet& s, int cta, int ctas, const int64_t* shift_ = nullptr)
-        : v(cta), stride(ctas), end(s.max_count * s.n), shift(shift_)
+        : v(cta), stride(ctas), end(s.max_count * s.n), route(pinned_route(s, cta)), shift(shift_)
     {
+        if (route >= 0) {
+            v      = cta - s.first[route];
+            stride = s.first[route + 1] - s.first[route];
+            end    = s.r[route].count;
+        }
     }
     __device__ bool next(const RouteSet& s, Chunk& c)
     {
         while (v < end) {
-            const int     ri  = static_cast<int>(v % s.n);
-            const int64_t idx = v / s.n;
+            const int     ri  = route >= 0 ? route : static_cast<int>(v % s.n);
+            const int64_t idx = route >= 0 ? v : v / s.n;
             v += stride;
             const RouteX& r = s.r[ri];
             if (idx >= r.count) {
@@ -144,13 +168,14 @@ __device__ void announce(const KArgs& a, uint64_t value, bool with_slot = false)
     }
 }
 
-// Called by one full warp. Lane p < world waits until rank p has announced at least `target`.
-// Returns false (on every lane) after the time limit, having recorded who was missing.
-__device__ bool await(const KArgs& a, uint64_t target, uint32_t code)
+// Called by one full warp. Lane p < world waits until rank p has announced at least `target`,
+// for the ranks named in `who` (bit p). Returns false (on every lane) after the time limit, having
+// recorded who was missing.
+__device__ bool await(const KArgs& a, uint64_t target, uint32_t code, uint32_t who = 0xffffffffu)
 {
     const int lane = threadIdx.x & 31;
     bool      ok   = true;
-    if (lane < a.world) {
+    if (lane < a.world && ((who >> lane) & 1u)) {
         const uint64_t t0    = globaltimer_ns();
         uint32_t       spins = 0;
         uint64_t       seen;
@@ -332,6 +357,15 @@ __global__ void __launch_bounds__(kBulk ? 32 : kLdstThreads, kBulk ? 1 : kLdstCt
     // this launch, its reads of its own window included, is finished; nobody overwrites a window
     // before its owner said so. Every CTA polls the (local) flags itself, so there is no grid-wide
     // dependency here.
+    // A CTA pinned to one route writes one rank's memory only, so it waits for that rank alone and
+    // starts pushing the moment that rank has announced, however late the others are. A route
+    // whose destination is final (the own share going straight to the caller's tensor) touches
+    // no window and waits for nobody.
+    uint32_t  who = 0xffffffffu;
+    const int pin = pinned_route(a.push, blockIdx.x);
+    if (pin >= 0) {
+        who = a.push.r[pin].peer >= 0 ? (1u << a.push.r[pin].peer) : 0u;
+    }
     bool alive = true;
     if (handshake && warp == 0) {
         if (blockIdx.x == 0) {
@@ -340,13 +374,14 @@ __global__ void __launch_bounds__(kBulk ? 32 : kLdstThreads, kBulk ? 1 : kLdstCt
                 announce(a, base + 2);
             }
         }
-        alive = await(a, base + 1, FU_ST_OPEN_TIMEOUT);
+        alive = await(a, base + 1, FU_ST_OPEN_TIMEOUT, who);
     }
     if (warp == 0) {
         // Which buffer each rank wants this call's payload in: announced with the opening flag
-        // (the acquire in await() orders this read), or given by the host when there is no handshake.
+        // (the acquire in await() orders this read, so only the ranks waited for are read), or
+        // given by the host when there is no handshake.
         const int lane = threadIdx.x & 31;
-        if (lane < a.world) {
+        if (lane < a.world && ((who >> lane) & 1u)) {
             int slot = handshake ? static_cast<int>(*reinterpret_cast<volatile uint8_t*>(&own->slot_of[lane]))
                                  : static_cast<int>(a.peer_slot[lane]);
             if (slot < 0 || slot > a.n_pool) {
@@ -472,6 +507,55 @@ void decompose(RouteX& x, int64_t chunk)
     }
     x.row_groups = (x.rows + x.rows_per_chunk - 1) / x.rows_per_chunk;
     x.count      = x.batches * x.row_groups * x.pieces_per_row;
+}
+
+// Deals `ctas` CTAs to the routes of a set in proportion to what each route costs: its bytes, with
+// a route that stays on this device (the own share) counted at kLocalCost of a route that crosses
+// NVLink. Every route gets at least one CTA; with fewer CTAs than routes the set stays unpinned and
+// its chunks are dealt round-robin.
+constexpr double kLocalCost = 0.3;
+void pin_ctas(RouteSet& set, int ctas, int rank)
+{
+    set.pinned = 0;
+    if (set.n < 1 || ctas < set.n) {
+        return;
+    }
+    double cost[FU_MAX_WORLD], total = 0.0;
+    for (int g = 0; g < set.n; ++g) {
+        const RouteX& r     = set.r[g];
+        const bool    local = r.peer < 0 || r.peer == rank;
+        cost[g] = static_cast<double>(r.row_bytes) * static_cast<double>(r.rows) * static_cast<double>(r.batches)
+                  * (local ? kLocalCost : 1.0);
+        total += cost[g];
+    }
+    int given[FU_MAX_WORLD], sum = 0;
+    for (int g = 0; g < set.n; ++g) {
+        given[g] = std::max(1, static_cast<int>(ctas * cost[g] / total));
+        sum += given[g];
+    }
+    // hand the remainder (or take the excess) one CTA at a time where it changes the load per CTA most
+    while (sum != ctas) {
+        int best = -1;
+        for (int g = 0; g < set.n; ++g) {
+            if (sum > ctas && given[g] <= 1) {
+                continue;
+            }
+            const double load = cost[g] / given[g];
+            if (best < 0 || (sum < ctas ? load > cost[best] / given[best] : load < cost[best] / given[best])) {
+                best = g;
+            }
+        }
+        if (best < 0) {
+            return;  // cannot happen with ctas >= n; stay unpinned rather than guess
+        }
+        given[best] += sum < ctas ? 1 : -1;
+        sum += sum < ctas ? 1 : -1;
+    }
+    set.first[0] = 0;
+    for (int g = 0; g < set.n; ++g) {
+        set.first[g + 1] = static_cast<int16_t>(set.first[g] + given[g]);
+    }
+    set.pinned = 1;
 }
 
 bool aligned16(const void* p)
@@ -623,9 +707,7 @@ extern "C" int fu_a2a4d(const FuA2AArgs* args, void* stream_v)
     }
     int ctas = in.ctas > 0 ? std::min(in.ctas, share) : share;
     ctas     = std::max(1, ctas);
-    if (k.push.n > 1 && ctas > k.push.n) {
-        ctas -= ctas % k.push.n;  // a multiple of the route count pins each CTA to one peer
-    }
+    pin_ctas(k.push, ctas, in.rank);
     if (ldst) {
         a2a4d_kernel<false><<<ctas, kLdstThreads, 0, stream>>>(k);
     }

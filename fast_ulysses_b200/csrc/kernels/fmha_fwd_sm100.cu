@@ -5,7 +5,9 @@
 //   warp 0       TMA producer: Q (once per item), then K and V tiles through two-stage rings
 //   warp 1       MMA issuer: S_t = Q_t K^T (operands in shared memory), O_t += P_t V (P read
 //                from tensor memory, V as an MN-major shared-memory operand)
-//   warps 2..5   softmax for query tile 0, warps 6..9 for query tile 1: one thread per row;
+//   warps 2, 3   idle (they fill warpgroup 0 so that register counts can be set per warpgroup:
+//                warpgroup 0 gives registers away, the softmax warpgroups take them)
+//   warps 4..7   softmax for query tile 0, warps 8..11 for query tile 1: one thread per row;
 //                exp2 with a lazily updated reference maximum, P written back over S in tensor
 //                memory as packed bf16, O rescaled in tensor memory only when the maximum grew by
 //                more than 2^8; final normalisation, bf16 store and log-sum-exp
@@ -37,8 +39,11 @@ constexpr int KV_STAGES = 2;
 constexpr int TILE_BYTES = 128 * D * 2;       // 32 KiB: a 128 x 128 bf16 tile as two 64-column halves
 constexpr int HALF_BYTES = TILE_BYTES / 2;
 constexpr int SMEM_BYTES = (QT + 2 * KV_STAGES) * TILE_BYTES + 1024;
-constexpr int THREADS    = 32 * 10;
+constexpr int THREADS    = 32 * 12;            // three warpgroups: {producer, MMA, 2 idle}, softmax 0, softmax 1
+constexpr int REGS_SMALL = 104;                 // warpgroup 0 after it has given registers away
+constexpr int REGS_SOFTMAX = 200;              // per scheduler: 32 x (104 + 2 x 200) = 16128 of 16384 registers
 constexpr float RESCALE_THRESHOLD = 8.0f;     // in log2 units
+constexpr int   kPolyPairs = 0;               // of every 16 exponential pairs, on the FMA pipe by default
 
 enum : uint32_t { ERR_LOAD = 11, ERR_MMA = 12, ERR_SOFTMAX = 13 };
 
@@ -51,6 +56,7 @@ struct Params {
     int            q_blocks, total_work, n_kv;
     float          scale, scale_log2;
     uint32_t*      err;
+    uint64_t*      trace;
 };
 
 __device__ __forceinline__ void flag(const Params& p, uint32_t code)
@@ -63,9 +69,64 @@ __device__ __forceinline__ void flag(const Params& p, uint32_t code)
 struct Barriers {
     uint64_t q_full, q_empty;
     uint64_t k_full[KV_STAGES], k_empty[KV_STAGES], v_full[KV_STAGES], v_empty[KV_STAGES];
-    uint64_t s_full[QT], p_ready[QT], o_final[QT], o_free[QT];
+    uint64_t s_full[QT], p_lo[QT], p_hi[QT], o_final[QT], o_free[QT];
 };
 
+// exp2 of a pair on the FMA pipe instead of the special-function unit: floor by a round-down add of
+// 1.5 * 2^23 (the integer part lands in the low mantissa bits), a cubic for 2^fraction (relative
+// error 7.5e-5, far below the bf16 rounding of P that follows), and the integer part added to the
+// exponent field. Arguments below -126 are clamped: their exponent field would wrap.
+__device__ __forceinline__ void ex2_poly2(float& e0, float& e1, float x0, float x1)
+{
+    constexpr float MAGIC = 12582912.0f;
+    constexpr float C0 = 0.9999251961708069f, C1 = 0.695833683013916f, C2 = 0.22606723010540009f,
+                    C3 = 0.07802422344684601f;
+    x0 = fmaxf(x0, -126.0f);
+    x1 = fmaxf(x1, -126.0f);
+    float t0, t1, i0, i1, f0, f1, p0, p1;
+    ptx::add2_rm(t0, t1, x0, x1, MAGIC, MAGIC);
+    ptx::add2(i0, i1, t0, t1, -MAGIC, -MAGIC);
+    ptx::fma2(f0, f1, i0, i1, -1.0f, -1.0f, x0, x1);
+    ptx::fma2(p0, p1, f0, f1, C3, C3, C2, C2);
+    ptx::fma2(p0, p1, p0, p1, f0, f1, C1, C1);
+    ptx::fma2(p0, p1, p0, p1, f0, f1, C0, C0);
+    e0 = __uint_as_float(__float_as_uint(p0) + (__float_as_uint(t0) << 23));
+    e1 = __uint_as_float(__float_as_uint(p1) + (__float_as_uint(t1) << 23));
+}
+
+// 32 columns of one row: P = exp2(S * c - m * c) as packed bf16, row sum into l4. NP of every 16
+// pairs take the FMA-pipe path (spread evenly so both pipes stay fed), the rest the special-function unit.
+template <int NP>
+__device__ __forceinline__ void exp_chunk(const uint32_t* r, float c, float nmc, float (&l4)[4], uint32_t (&pk)[16])
+{
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        float x0, x1, e0, e1;
+        ptx::fma2(x0, x1, __uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]), c, c, nmc, nmc);
+        if (NP > 0 && (i * NP) % 16 < NP) {
+            ex2_poly2(e0, e1, x0, x1);
+        }
+        else {
+            e0 = ptx::ex2(x0);
+            e1 = ptx::ex2(x1);
+        }
+        ptx::add2(l4[(2 * i) & 3], l4[(2 * i + 1) & 3], l4[(2 * i) & 3], l4[(2 * i + 1) & 3], e0, e1);
+        pk[i] = ptx::pack_bf16x2(e0, e1);
+    }
+}
+
+// Optional timeline (TRACE builds only): CTA 0 stores the SM clock of pipeline events of kv steps
+// 64..71 of its first work item, 32 slots per step: 0..9 softmax tile 0, 10..19 softmax tile 1,
+// 20..31 the MMA issuer.
+template <bool TRACE>
+__device__ __forceinline__ void stamp(const Params& p, uint32_t step, int ev)
+{
+    if (TRACE && blockIdx.x == 0 && (threadIdx.x & 31) == 0 && step >= 64u && step < 72u) {
+        p.trace[(step - 64u) * 32 + ev] = clock64();
+    }
+}
+
+template <int NP, bool TRACE>
 __global__ void __launch_bounds__(THREADS, 1) fmha_fwd_kernel(const __grid_constant__ Params p)
 {
     extern __shared__ uint8_t smem_raw[];
@@ -96,7 +157,8 @@ __global__ void __launch_bounds__(THREADS, 1) fmha_fwd_kernel(const __grid_const
         }
         for (int t = 0; t < QT; ++t) {
             ptx::mbar_init(&bar.s_full[t], 1);
-            ptx::mbar_init(&bar.p_ready[t], 4);  // one arrival per warp
+            ptx::mbar_init(&bar.p_lo[t], 4);  // one arrival per warp
+            ptx::mbar_init(&bar.p_hi[t], 4);
             ptx::mbar_init(&bar.o_final[t], 1);
             ptx::mbar_init(&bar.o_free[t], 4);
         }
@@ -115,6 +177,8 @@ __global__ void __launch_bounds__(THREADS, 1) fmha_fwd_kernel(const __grid_const
     const uint32_t tmem = tmem_holder;
     const int      n_kv = p.n_kv;
 
+    if (warp < 4) {
+    ptx::setmaxnreg_dec<REGS_SMALL>();
     if (warp == 0) {
         // ---------------------------------------------------------------- producer
         if (lane == 0) {
@@ -188,12 +252,15 @@ __global__ void __launch_bounds__(THREADS, 1) fmha_fwd_kernel(const __grid_const
                 }
                 ptx::mma_commit(&bar.s_full[t]);
             };
-            auto issue_pv = [&](int t, int stage, bool accumulate) {
+            // One half (64 kv rows) of P_t V: the softmax hands P over in two halves so that the
+            // first half's products run under the second half's exponentials.
+            auto issue_pv = [&](int t, int stage, int half, bool accumulate) {
                 // 16 kv rows = 2048 bytes further down; the two 64-wide halves of d are HALF_BYTES
                 // apart (leading byte offset), 8-row groups 1024 bytes apart
                 const uint64_t va = ptx::desc_advance(desc_v, stage * TILE_BYTES);
 #pragma unroll
-                for (int kk = 0; kk < BN / 16; ++kk) {
+                for (int k4 = 0; k4 < BN / 32; ++k4) {
+                    const int kk = half * (BN / 32) + k4;
                     ptx::mma_f16_ts(tmem + 256 + t * 128, tmem + t * 128 + kk * 8, ptx::desc_advance(va, kk * 2048),
                                     idesc_pv, accumulate || kk != 0);
                 }
@@ -231,25 +298,37 @@ __global__ void __launch_bounds__(THREADS, 1) fmha_fwd_kernel(const __grid_const
                         break;
                     }
                     for (int t = 0; t < QT; ++t) {
-                        if (!ptx::mbar_wait(&bar.p_ready[t], pcount[t] & 1u)) {
+                        stamp<TRACE>(p, it, 20 + t * 6 + 0);
+                        if (!ptx::mbar_wait(&bar.p_lo[t], pcount[t] & 1u)) {
                             flag(p, ERR_MMA);
                             ok = false;
                             break;
                         }
-                        ++pcount[t];
+                        stamp<TRACE>(p, it, 20 + t * 6 + 1);
                         if (j == 0 && !ptx::mbar_wait(&bar.o_free[t], (wc & 1u) ^ 1u)) {
                             flag(p, ERR_MMA);
                             ok = false;
                             break;
                         }
                         ptx::tc_fence_after();
-                        issue_pv(t, s, j != 0);
+                        issue_pv(t, s, 0, j != 0);
+                        stamp<TRACE>(p, it, 20 + t * 6 + 2);
+                        if (!ptx::mbar_wait(&bar.p_hi[t], pcount[t] & 1u)) {
+                            flag(p, ERR_MMA);
+                            ok = false;
+                            break;
+                        }
+                        stamp<TRACE>(p, it, 20 + t * 6 + 3);
+                        ++pcount[t];
+                        ptx::tc_fence_after();
+                        issue_pv(t, s, 1, true);
                         if (!more) {
                             ptx::mma_commit(&bar.o_final[t]);
                         }
                         else {
                             issue_qk(t, sn);  // S_t is free again: PV_t above is ordered before it
                         }
+                        stamp<TRACE>(p, it, 20 + t * 6 + 4);
                     }
                     if (!ok) {
                         break;
@@ -264,9 +343,11 @@ __global__ void __launch_bounds__(THREADS, 1) fmha_fwd_kernel(const __grid_const
         }
         __syncwarp();
     }
+    }
     else {
+        ptx::setmaxnreg_inc<REGS_SOFTMAX>();
         // ---------------------------------------------------------------- softmax + epilogue
-        const int      t       = (warp - 2) >> 2;          // query tile
+        const int      t       = (warp - 4) >> 2;          // query tile
         const int      quarter = warp & 3;                 // TMEM lane quarter of this warp
         const int      row_in  = quarter * 32 + lane;      // row inside the query tile
         const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
@@ -290,6 +371,7 @@ __global__ void __launch_bounds__(THREADS, 1) fmha_fwd_kernel(const __grid_const
                     break;
                 }
                 ptx::tc_fence_after();
+                stamp<TRACE>(p, scount, t * 10 + 0);
                 const int valid = min(BN, p.Skv - j * BN);  // columns of this step that exist
                 // The whole row of S in registers with a single wait: the softmax sits on the
                 // critical path between two MMAs, so its latency matters more than its register use.
@@ -299,6 +381,7 @@ __global__ void __launch_bounds__(THREADS, 1) fmha_fwd_kernel(const __grid_const
                     ptx::tmem_ld_32x32(ts + ch * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[ch * 32]));
                 }
                 ptx::tmem_ld_wait();
+                stamp<TRACE>(p, scount, t * 10 + 1);
                 if (valid < BN) {
 #pragma unroll
                     for (int i = 0; i < BN; ++i) {
@@ -307,12 +390,13 @@ __global__ void __launch_bounds__(THREADS, 1) fmha_fwd_kernel(const __grid_const
                         }
                     }
                 }
+                // row maximum with three-input max: 64 instructions in four independent chains
                 float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-                for (int i = 0; i < BN; i += 4) {
+                for (int i = 0; i < BN; i += 8) {
 #pragma unroll
                     for (int u = 0; u < 4; ++u) {
-                        mx4[u] = fmaxf(mx4[u], __uint_as_float(r[i + u]));
+                        mx4[u] = ptx::max3(mx4[u], __uint_as_float(r[i + 2 * u]), __uint_as_float(r[i + 2 * u + 1]));
                     }
                 }
                 const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
@@ -337,28 +421,49 @@ __global__ void __launch_bounds__(THREADS, 1) fmha_fwd_kernel(const __grid_const
                 if (grow) {
                     m_ref = mx;
                 }
+                stamp<TRACE>(p, scount, t * 10 + 2);
                 const float mc = m_ref * c;
                 // P = exp2(S * c - m_ref * c), written over S as packed bf16
                 const float nmc = -mc;
                 float       l4[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-                for (int ch = 0; ch < 4; ++ch) {
-                    uint32_t pk[16];
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        float x0, x1;
-                        ptx::fma2(x0, x1, __uint_as_float(r[ch * 32 + 2 * i]), __uint_as_float(r[ch * 32 + 2 * i + 1]), c, c,
-                                  nmc, nmc);
-                        const float e0 = ptx::ex2(x0), e1 = ptx::ex2(x1);
-                        ptx::add2(l4[(2 * i) & 3], l4[(2 * i + 1) & 3], l4[(2 * i) & 3], l4[(2 * i + 1) & 3], e0, e1);
-                        pk[i] = ptx::pack_bf16x2(e0, e1);
-                    }
-                    ptx::tmem_st_32x16(ts + ch * 16, pk);
+                // The last block of a ragged sequence holds -inf columns: those take the
+                // special-function unit only (the FMA-pipe form clamps instead of returning 0).
+                uint32_t pk[16];
+                if (valid == BN) {
+                    exp_chunk<NP>(&r[0], c, nmc, l4, pk);
+                    ptx::tmem_st_32x16(ts, pk);
+                    exp_chunk<NP>(&r[32], c, nmc, l4, pk);
+                    ptx::tmem_st_32x16(ts + 16, pk);
+                    // third quarter's exponentials are issued before waiting for the first half's
+                    // stores, so the store latency hides under them
+                    exp_chunk<NP>(&r[64], c, nmc, l4, pk);
                 }
-                l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
+                else {
+                    exp_chunk<0>(&r[0], c, nmc, l4, pk);
+                    ptx::tmem_st_32x16(ts, pk);
+                    exp_chunk<0>(&r[32], c, nmc, l4, pk);
+                    ptx::tmem_st_32x16(ts + 16, pk);
+                    exp_chunk<0>(&r[64], c, nmc, l4, pk);
+                }
+                stamp<TRACE>(p, scount, t * 10 + 3);
                 ptx::tmem_st_wait();
                 ptx::tc_fence_before();
-                ptx::mbar_arrive_warp(&bar.p_ready[t]);
+                ptx::mbar_arrive_warp(&bar.p_lo[t]);
+                stamp<TRACE>(p, scount, t * 10 + 4);
+                ptx::tmem_st_32x16(ts + 32, pk);
+                if (valid == BN) {
+                    exp_chunk<NP>(&r[96], c, nmc, l4, pk);
+                }
+                else {
+                    exp_chunk<0>(&r[96], c, nmc, l4, pk);
+                }
+                ptx::tmem_st_32x16(ts + 48, pk);
+                l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
+                stamp<TRACE>(p, scount, t * 10 + 5);
+                ptx::tmem_st_wait();
+                ptx::tc_fence_before();
+                ptx::mbar_arrive_warp(&bar.p_hi[t]);
+                stamp<TRACE>(p, scount, t * 10 + 6);
             }
             if (!ok) {
                 break;
@@ -451,14 +556,37 @@ extern "C" int fu_fmha_fwd(const FuFmhaArgs* a, void* stream)
     int dev = 0, sms = 0;
     FU_CUDA_OK(cudaGetDevice(&dev));
     FU_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-    static bool configured[64] = {};
-    if (dev < 64 && !configured[dev]) {
-        FU_CUDA_OK(cudaFuncSetAttribute(fmha_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-        configured[dev] = true;
-    }
     int grid = a->ctas > 0 ? std::min(a->ctas, sms) : sms;
     grid     = std::max(1, std::min(grid, p.total_work));
-    fmha_fwd_kernel<<<grid, THREADS, SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(p);
-    FU_CUDA_OK(cudaGetLastError());
-    return FU_OK;
+    // how many of every 16 exponential pairs go to the FMA pipe: FU_FMHA_POLY(n) in flags, default kPolyPairs
+    const int np = (a->flags & FU_FMHA_POLY_SET) ? ((a->flags >> 8) & 15) : kPolyPairs;
+    if (np < 0 || np > 6 || (np & 1)) {
+        return fu::fail(FU_E_ARG, "fu_fmha_fwd: %d of 16 exponential pairs on the FMA pipe is not built (0, 2, 4, 6)", np);
+    }
+    static bool configured[64][8] = {};
+    auto launch = [&](auto kernel) -> int {
+        if (dev >= 64 || a->trace || !configured[dev][np]) {
+            FU_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+            if (dev < 64) {
+                configured[dev][np] = true;
+            }
+        }
+        kernel<<<grid, THREADS, SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(p);
+        FU_CUDA_OK(cudaGetLastError());
+        return FU_OK;
+    };
+    p.trace = a->trace;
+    if (a->trace) {
+        if (np != 0) {
+            return fu::fail(FU_E_ARG, "fu_fmha_fwd: the timeline build exists for the default exponential split only");
+        }
+        return launch(fmha_fwd_kernel<0, true>);
+    }
+    switch (np) {
+    case 0: return launch(fmha_fwd_kernel<0, false>);
+    case 2: return launch(fmha_fwd_kernel<2, false>);
+    case 4: return launch(fmha_fwd_kernel<4, false>);
+    case 6: return launch(fmha_fwd_kernel<6, false>);
+    default: return fu::fail(FU_E_ARG, "fu_fmha_fwd: %d of 16 exponential pairs on the FMA pipe is not built (0, 2, 4, 6)", np);
+    }
 }

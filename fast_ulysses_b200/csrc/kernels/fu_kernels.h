@@ -215,6 +215,10 @@ FU_API int fu_pull_outproj(const FuPullArgs* args, void* stream);
 // Backward: two passes without atomics (bit-reproducible dQ, about 1.5x the time of the default
 // single pass, which sums dQ over the K/V blocks with fp32 reductions).
 enum { FU_FMHA_DETERMINISTIC = 1 };
+// Forward tuning knob: FU_FMHA_POLY(n) computes n of every 16 exponential pairs on the FMA pipe
+// (a cubic) instead of the special-function unit; n in {0, 2, 4, 6}. Without it the library default applies.
+#define FU_FMHA_POLY_SET 0x1000
+#define FU_FMHA_POLY(n) (FU_FMHA_POLY_SET | (((n) & 15) << 8))
 typedef struct FuFmhaArgs {
     const void* q;
     const void* k;

@@ -369,6 +369,35 @@ __device__ __forceinline__ void add2(float& d0, float& d1, float a0, float a1, f
         : "=f"(d0), "=f"(d1)
         : "f"(a0), "f"(a1), "f"(b0), "f"(b1));
 }
+// Per-warpgroup register budget (all four warps of a warpgroup execute it): a warpgroup of light
+// warps gives registers back, the heavy ones take them.
+template <int N>
+__device__ __forceinline__ void setmaxnreg_inc()
+{
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N>
+__device__ __forceinline__ void setmaxnreg_dec()
+{
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+// round-down add of a pair: floor(x) by adding 1.5 * 2^23
+__device__ __forceinline__ void add2_rm(float& d0, float& d1, float a0, float a1, float b0, float b1)
+{
+    asm("{\n\t.reg .b64 ra, rb, rd;\n\t"
+        "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+        "add.rm.ftz.f32x2 rd, ra, rb;\n\t"
+        "mov.b64 {%0, %1}, rd;\n\t}"
+        : "=f"(d0), "=f"(d1)
+        : "f"(a0), "f"(a1), "f"(b0), "f"(b1));
+}
+// three-input maximum (sm_100): halves the instruction count of a row maximum
+__device__ __forceinline__ float max3(float a, float b, float c)
+{
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
 __device__ __forceinline__ float ex2(float x)
 {
     float y;

@@ -153,7 +153,15 @@ Prepared prepare(Group& g, const at::Tensor& input, int64_t mode, const Splits& 
                 // still referenced by a live tensor, this rank alone falls back to window + copy-out.
                 p.pool_slot = g.take_pool_slot(window_bytes, cur);
                 if (p.pool_slot > 0) {
-                    p.output = g.pool_output(p.pool_slot, p.plan->out_shape, dtype);
+                    // the buffer is marked busy from here; only the tensor's deleter clears the mark,
+                    // so a failure before the tensor exists must clear it by hand
+                    try {
+                        p.output = g.pool_output(p.pool_slot, p.plan->out_shape, dtype);
+                    }
+                    catch (...) {
+                        g.release_pool_slot(p.pool_slot);
+                        throw;
+                    }
                 }
             }
             if (!p.output.defined()) {

@@ -289,8 +289,17 @@ int Group::take_pool_slot(int64_t bytes, void* stream)
                 const c10::cuda::CUDAGuard guard(static_cast<c10::DeviceIndex>(device_index_));
                 cudaEvent_t ev = nullptr;
                 cuda_ok(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming), "cudaEventCreateWithFlags");
-                cuda_ok(cudaEventRecord(ev, static_cast<cudaStream_t>(s.last_stream)), "cudaEventRecord");
-                cuda_ok(cudaStreamWaitEvent(static_cast<cudaStream_t>(stream), ev, 0), "cudaStreamWaitEvent");
+                // `last_stream` is only a handle: the caller may have destroyed that stream since.
+                // A stream that no longer exists has nothing queued, but CUDA refuses the handle; a
+                // rank that threw here would leave its peers waiting in the collective, so fall
+                // back to waiting for the whole device instead.
+                if (cudaEventRecord(ev, static_cast<cudaStream_t>(s.last_stream)) == cudaSuccess) {
+                    cuda_ok(cudaStreamWaitEvent(static_cast<cudaStream_t>(stream), ev, 0), "cudaStreamWaitEvent");
+                }
+                else {
+                    (void)cudaGetLastError();
+                    cuda_ok(cudaDeviceSynchronize(), "cudaDeviceSynchronize");
+                }
                 cuda_ok(cudaEventDestroy(ev), "cudaEventDestroy");
             }
             s.last_stream = stream;
@@ -300,6 +309,13 @@ int Group::take_pool_slot(int64_t bytes, void* stream)
         }
     }
     return 0;
+}
+
+void Group::release_pool_slot(int slot)
+{
+    if (slot >= 1 && slot <= static_cast<int>(pool_.size())) {
+        pool_[static_cast<size_t>(slot - 1)].busy->store(0);
+    }
 }
 
 at::Tensor Group::pool_output(int slot, at::IntArrayRef shape, at::ScalarType dtype)

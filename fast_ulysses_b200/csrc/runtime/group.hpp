@@ -81,6 +81,8 @@ public:
     // none (the call then goes through the window and is copied out, on this rank only).
     int           take_pool_slot(int64_t bytes, void* stream);
     at::Tensor    pool_output(int slot, at::IntArrayRef shape, at::ScalarType dtype);
+    // Gives back a buffer taken with take_pool_slot for which no tensor came to exist.
+    void          release_pool_slot(int slot);
     bool          output_pool() const { return pool_enabled_; }
     void          set_output_pool(bool on) { pool_enabled_ = on; }
     int64_t       pool_hits() const { return pool_hits_; }

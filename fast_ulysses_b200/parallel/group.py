@@ -136,6 +136,18 @@ class UlyssesGroup:
         ``seq_splits[p]`` / ``head_splits[p]`` are rank p's shards: both or neither, identical on
         every rank. Differentiable (the backward is the other mode with the same splits) unless
         ``out=`` is given.
+
+        Ownership of the returned tensor. By default the result lives in one of three pooled
+        symmetric buffers that the peers wrote directly; it behaves like any tensor (views keep it
+        alive, it survives ``destroy()``), and its buffer returns to the pool when the last
+        reference is dropped. Two rules follow from the memory not belonging to the caching
+        allocator: ``Tensor.record_stream()`` has NO effect on it, and a later call on the same
+        group may hand the buffer to the peers again as soon as the tensor is dropped. Readers
+        queued on the stream that made the call (and on the stream of the next call) are ordered
+        automatically; a reader on any other stream must be ordered by the caller before the
+        tensor is dropped (``torch.cuda.current_stream().wait_stream(side)``), or the pool
+        switched off on every rank with ``set_output_pool(False)``, which restores window +
+        copy-out into an ordinary allocation.
         """
         if out is None:
             return _OPS.all_to_all_4d(self._handle, x, mode, seq_splits, head_splits)
@@ -157,7 +169,7 @@ class UlyssesGroup:
         seq_splits: list[int] | None = None,
         head_splits: list[int] | None = None,
         lend: bool = False,
-        stage: bool = False,
+        stage: bool = True,
     ):
         """``all_to_all_4d`` on the group's high-priority comm stream, returning immediately.
 
@@ -166,10 +178,12 @@ class UlyssesGroup:
         four windows the group rotates through (no copy-out, at most four results alive at once).
         Not differentiable.
 
-        The kernel reads ``x`` in place on the comm stream (there is no staging copy), and the
-        caching allocator is told about the cross-stream use, so freeing ``x`` is safe. Writing
-        into ``x`` on the caller's stream before waiting on the result is not ordered against the
-        transfer; pass ``stage=True`` to have the call take a private copy first.
+        ``x`` may be overwritten or freed the moment this returns: by default the call first takes
+        a private copy of ``x`` on the caller's stream (``stage=True``, the reference's contract,
+        src/group.cc:320-404 there). ``stage=False`` skips that copy and lets the kernel read ``x``
+        in place on the comm stream: freeing ``x`` is still safe (the caching allocator is told
+        about the cross-stream use), but writing into ``x`` on the caller's stream before waiting
+        on the result is then a race the library cannot see.
         """
         if out is not None and lend:
             raise ValueError(

@@ -26,6 +26,21 @@ def test_forward_matches_fp32(b, h, sq, skv):
     assert torch.allclose(lse, lse_ref, atol=2e-2, rtol=1e-3), (lse - lse_ref).abs().max().item()
 
 
+@pytest.mark.parametrize("poly", [0, 2, 4, 6])
+def test_forward_exponentials_split_between_the_pipes(poly):
+    """Part of the exponentials as a cubic on the FMA pipe: same result within bf16 rounding,
+    for scores whose spread reaches the clamp of the cubic's argument."""
+    torch.manual_seed(11)
+    q = (torch.randn(1, 300, 2, 128, device="cuda") * 3).bfloat16()
+    k = (torch.randn(1, 700, 2, 128, device="cuda") * 3).bfloat16()
+    v = torch.randn(1, 700, 2, 128, device="cuda").bfloat16()
+    o, lse = attention.fmha_fwd(q, k, v, poly=poly)
+    gemm.check_errors()
+    o_ref, lse_ref = attention.attention_reference(q, k, v)
+    assert rel_err(o, o_ref) < 1.5e-2, rel_err(o, o_ref)
+    assert torch.allclose(lse, lse_ref, atol=2e-2, rtol=1e-3), (lse - lse_ref).abs().max().item()
+
+
 def test_large_scores_exercise_the_lazy_rescale():
     torch.manual_seed(3)
     q = (torch.randn(1, 256, 1, 128, device="cuda") * 4).bfloat16()
