@@ -565,7 +565,19 @@ bool aligned16(const void* p)
 
 }  // namespace
 
-extern "C" int fu_a2a4d(const FuA2AArgs* args, void* stream_v)
+namespace {
+
+// One past the last byte a route touches on one side, relative to that side's base.
+int64_t route_extent(int64_t off, int64_t pitch, int64_t batch_stride, const FuRoute& r)
+{
+    if (r.rows <= 0 || r.batches <= 0 || r.row_bytes <= 0) {
+        return 0;
+    }
+    return off + (r.batches - 1) * batch_stride + (r.rows - 1) * pitch + r.row_bytes;
+}
+
+// Everything fu_a2a4d refuses, and the kernel arguments when it refuses nothing. Host arithmetic only.
+int build_args(const FuA2AArgs* args, KArgs& k)
 {
     if (!args) {
         return fu::fail(FU_E_ARG, "fu_a2a4d: null args");
@@ -577,7 +589,6 @@ extern "C" int fu_a2a4d(const FuA2AArgs* args, void* stream_v)
     if (in.n_routes < 0 || in.n_routes > FU_MAX_WORLD) {
         return fu::fail(FU_E_ARG, "fu_a2a4d: %d routes", in.n_routes);
     }
-    KArgs k{};
     k.rank       = in.rank;
     k.world      = in.world;
     k.flags      = in.flags;
@@ -651,8 +662,36 @@ extern "C" int fu_a2a4d(const FuA2AArgs* args, void* stream_v)
         if (!aligned16(in.peer_win[r.peer])) {
             return fu::fail(FU_E_ARG, "fu_a2a4d: rank %d's window is not 16-byte aligned", r.peer);
         }
+        if ((r.src_off | r.dst_off | r.src_pitch | r.dst_pitch | r.src_batch | r.dst_batch) < 0) {
+            return fu::fail(FU_E_ARG, "fu_a2a4d: route %d has a negative offset or stride", i);
+        }
         // The own share never needs the window when the caller wants the result elsewhere.
         const bool direct = copy_out && in.own_direct && r.peer == in.rank;
+        {
+            const int64_t src_end = route_extent(r.src_off, r.src_pitch, r.src_batch, r);
+            const int64_t dst_end = route_extent(r.dst_off, r.dst_pitch, r.dst_batch, r);
+            if (src_end > in.src_bytes) {
+                return fu::fail(FU_E_ARG, "fu_a2a4d: route %d reads up to byte %lld of an input of %lld bytes", i,
+                                (long long)src_end, (long long)in.src_bytes);
+            }
+            if (direct) {
+                if (dst_end > in.out_bytes) {
+                    return fu::fail(FU_E_ARG, "fu_a2a4d: route %d writes up to byte %lld of an output of %lld bytes", i,
+                                    (long long)dst_end, (long long)in.out_bytes);
+                }
+            }
+            else {
+                if (dst_end > in.win_bytes) {
+                    return fu::fail(FU_E_ARG, "fu_a2a4d: route %d writes up to byte %lld of rank %d's window of %lld bytes",
+                                    i, (long long)dst_end, r.peer, (long long)in.win_bytes);
+                }
+                // rank r.peer may ask for this call's payload in any of its pool buffers instead
+                if (in.n_pool > 0 && dst_end > in.pool_bytes) {
+                    return fu::fail(FU_E_ARG, "fu_a2a4d: route %d writes up to byte %lld but the pool buffers hold %lld bytes",
+                                    i, (long long)dst_end, (long long)in.pool_bytes);
+                }
+            }
+        }
         uint8_t*   dst    = direct ? static_cast<uint8_t*>(in.out) : static_cast<uint8_t*>(in.peer_win[r.peer]);
         // a route into another rank's memory follows that rank's choice of buffer for this call
         RouteX     x      = expand(r, static_cast<const uint8_t*>(in.src), dst, direct ? -1 : r.peer);
@@ -669,6 +708,15 @@ extern "C" int fu_a2a4d(const FuA2AArgs* args, void* stream_v)
                 if (!granular(in.out_routes[i])) {
                     return fu::fail(FU_E_ARG, "fu_a2a4d: copy-out route %d is not 16-byte granular", i);
                 }
+                {
+                    const FuRoute& r = in.out_routes[i];
+                    if ((r.src_off | r.dst_off | r.src_pitch | r.dst_pitch | r.src_batch | r.dst_batch) < 0
+                        || route_extent(r.src_off, r.src_pitch, r.src_batch, r) > in.win_bytes
+                        || route_extent(r.dst_off, r.dst_pitch, r.dst_batch, r) > in.out_bytes) {
+                        return fu::fail(FU_E_ARG, "fu_a2a4d: copy-out route %d leaves the window (%lld bytes) or the "
+                                        "output (%lld bytes)", i, (long long)in.win_bytes, (long long)in.out_bytes);
+                    }
+                }
                 RouteX x = expand(in.out_routes[i], win, static_cast<uint8_t*>(in.out));
                 if (x.count > 0) {
                     k.copy_out.r[k.copy_out.n++] = x;
@@ -677,6 +725,10 @@ extern "C" int fu_a2a4d(const FuA2AArgs* args, void* stream_v)
             }
         }
         else {
+            if (in.out_bytes > in.win_bytes) {
+                return fu::fail(FU_E_ARG, "fu_a2a4d: copy-out of %lld bytes from a window of %lld bytes",
+                                (long long)in.out_bytes, (long long)in.win_bytes);
+            }
             FuRoute flat{};
             flat.row_bytes = in.out_bytes;
             flat.rows = flat.batches = 1;
@@ -689,6 +741,26 @@ extern "C" int fu_a2a4d(const FuA2AArgs* args, void* stream_v)
     // `copy_out.n` doubles as "every CTA must see the closing handshake"; with nothing left to copy
     // (a single rank whose own share went straight to `out`) the plain closing path is taken.
 
+    return FU_OK;
+}
+
+}  // namespace
+
+extern "C" int fu_a2a4d_check(const FuA2AArgs* args)
+{
+    KArgs k{};
+    return build_args(args, k);
+}
+
+extern "C" int fu_a2a4d(const FuA2AArgs* args, void* stream_v)
+{
+    KArgs     k{};
+    const int rc = build_args(args, k);
+    if (rc != FU_OK) {
+        return rc;
+    }
+    const FuA2AArgs& in   = *args;
+    const bool       ldst = (in.flags & FU_A2A_LDST) != 0;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
     int          dev = 0, sms = 0;
     FU_CUDA_OK(cudaGetDevice(&dev));

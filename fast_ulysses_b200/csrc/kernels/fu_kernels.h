@@ -99,9 +99,19 @@ typedef struct FuA2AArgs {
     int32_t     n_pool;
     int32_t     my_slot;
     int8_t      peer_slot[FU_MAX_WORLD];
+    // Capacities (append-only fields), in bytes: of every rank's window, of every pool buffer and of
+    // the readable extent behind `src`. The launcher computes the last byte every route reads and
+    // writes and refuses the launch when one lies beyond its buffer: a route is an address formula
+    // applied to another GPU's memory, and nothing on the device would catch a wrong one.
+    int64_t     win_bytes;
+    int64_t     pool_bytes;
+    int64_t     src_bytes;
 } FuA2AArgs;
 
 FU_API int fu_a2a4d(const FuA2AArgs* args, void* stream);
+// The argument checks of fu_a2a4d alone (everything it would refuse), without launching anything:
+// no CUDA call is made, so it runs on a machine without a GPU.
+FU_API int fu_a2a4d_check(const FuA2AArgs* args);
 
 // Standalone cross-rank barrier on a window's control block (epoch += 1).
 FU_API int fu_barrier(FuCtrl* const* peer_ctrl, int rank, int world, uint32_t timeout_ms, int flags, void* stream);
@@ -160,8 +170,13 @@ typedef struct FuQkvArgs {
     int32_t      n_types, n_normed;
     void*        y_save;
     int64_t      ld_y;
+    // Bytes available behind every win_q / win_k / win_v base (append-only). The largest offset the
+    // epilogue can store to, ((batches * s_total - (s_total - seq_off - s_local)) * head_splits[p]) * 256,
+    // is checked against it before the launch.
+    int64_t      win_bytes;
 } FuQkvArgs;
 FU_API int fu_qkv_rope_scatter(const FuQkvArgs* args, void* stream);
+FU_API int fu_qkv_rope_scatter_check(const FuQkvArgs* args);  // the argument checks alone; no CUDA call
 
 // Backward of per-head RMSNorm -> RoPE for q and k. dq, dk: (m, heads, 128) bf16 dense; y: the
 // pre-norm projections saved by fu_qkv_rope_scatter; dy receives d(projection) for q at column 0
@@ -204,8 +219,13 @@ typedef struct FuPullArgs {
     int32_t      ctas;
     int32_t      pad_;
     uint32_t*    err;
+    // Capacities (append-only): bytes readable behind every peer_o base, bytes of `gather`, words of `ready`.
+    int64_t      o_bytes;
+    int64_t      gather_bytes;
+    int64_t      ready_words;
 } FuPullArgs;
 FU_API int fu_pull_outproj(const FuPullArgs* args, void* stream);
+FU_API int fu_pull_outproj_check(const FuPullArgs* args);  // the argument checks alone; no CUDA call
 
 // ---- flash attention (head_dim 128, non-causal, bf16) -----------------------------------------------
 // q, k, v, o are addressed as (batch, seq, head, 128) with explicit element strides for the seq, head

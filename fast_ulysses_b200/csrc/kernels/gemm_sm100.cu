@@ -524,7 +524,7 @@ extern "C" int fu_gemm_bf16(const FuGemmArgs* g, void* stream)
     return FU_OK;
 }
 
-extern "C" int fu_qkv_rope_scatter(const FuQkvArgs* q, void* stream)
+extern "C" int fu_qkv_rope_scatter_check(const FuQkvArgs* q)
 {
     if (!q || !q->x || !q->w) {
         return fu::fail(FU_E_ARG, "fu_qkv_rope_scatter: null operand");
@@ -547,8 +547,46 @@ extern "C" int fu_qkv_rope_scatter(const FuQkvArgs* q, void* stream)
         return fu::fail(FU_E_ARG, "fu_qkv_rope_scatter: m=%lld is not a multiple of s_local=%lld", (long long)q->m,
                         (long long)q->s_local);
     }
+    int heads_seen = 0;
+    for (int p = 0; p < q->world; ++p) {
+        if (q->head_splits[p] < 0 || q->head_splits[p] > 255) {
+            return fu::fail(FU_E_ARG, "fu_qkv_rope_scatter: head_splits[%d]=%d", p, q->head_splits[p]);
+        }
+        heads_seen += q->head_splits[p];
+        if (!q->win_q[p] || (n_types > 1 && !q->win_k[p]) || (n_types > 2 && !q->win_v[p]) || !q->peer_ctrl[p]) {
+            return fu::fail(FU_E_ARG, "fu_qkv_rope_scatter: no window for rank %d", p);
+        }
+    }
+    if (heads_seen != q->heads) {
+        return fu::fail(FU_E_ARG, "fu_qkv_rope_scatter: head_splits sum to %d, expected %d", heads_seen, q->heads);
+    }
+    // The epilogue stores row (batch, seq_off + s) of head `local` of rank p at
+    // ((batch * s_total + seq_off + s) * head_splits[p] + local) * 256 bytes behind that rank's base.
+    if (q->seq_off < 0 || q->s_total <= 0 || q->seq_off + q->s_local > q->s_total) {
+        return fu::fail(FU_E_ARG, "fu_qkv_rope_scatter: rows %lld..%lld do not lie inside a sequence of %lld",
+                        (long long)q->seq_off, (long long)(q->seq_off + q->s_local), (long long)q->s_total);
+    }
+    const int64_t batches = q->m / q->s_local;
+    for (int p = 0; p < q->world; ++p) {
+        const int64_t last = ((batches - 1) * q->s_total + q->seq_off + q->s_local) * q->head_splits[p] * 256;
+        if (q->head_splits[p] > 0 && last > q->win_bytes) {
+            return fu::fail(FU_E_ARG, "fu_qkv_rope_scatter: the stores to rank %d reach byte %lld of windows of %lld bytes",
+                            p, (long long)last, (long long)q->win_bytes);
+        }
+    }
+    return FU_OK;
+}
+
+extern "C" int fu_qkv_rope_scatter(const FuQkvArgs* q, void* stream)
+{
+    int rc = fu_qkv_rope_scatter_check(q);
+    if (rc != FU_OK) {
+        return rc;
+    }
+    const int n_types  = q->n_types > 0 ? q->n_types : 3;
+    const int n_normed = q->n_types > 0 ? q->n_normed : 2;
     QkvArgs a{};
-    int     rc = fill_core(a.core, q->x, q->w, q->m, static_cast<int64_t>(n_types) * q->heads * HEAD_DIM, q->k, q->ldx, q->ldw,
+    rc = fill_core(a.core, q->x, q->w, q->m, static_cast<int64_t>(n_types) * q->heads * HEAD_DIM, q->k, q->ldx, q->ldw,
                            q->err);
     if (rc != FU_OK) {
         return rc;
@@ -610,7 +648,7 @@ extern "C" int fu_qkv_rope_scatter(const FuQkvArgs* q, void* stream)
     return FU_OK;
 }
 
-extern "C" int fu_pull_outproj(const FuPullArgs* q, void* stream_v)
+extern "C" int fu_pull_outproj_check(const FuPullArgs* q)
 {
     if (!q || !q->w || !q->c || !q->gather || !q->ready) {
         return fu::fail(FU_E_ARG, "fu_pull_outproj: null operand");
@@ -624,6 +662,47 @@ extern "C" int fu_pull_outproj(const FuPullArgs* q, void* stream_v)
     }
     if ((q->ldc % 8) || (reinterpret_cast<uintptr_t>(q->c) & 15u)) {
         return fu::fail(FU_E_ARG, "fu_pull_outproj: C needs 16-byte aligned rows");
+    }
+    int heads_seen = 0;
+    for (int p = 0; p < q->world; ++p) {
+        if (q->head_splits[p] < 0 || q->head_splits[p] > 255 || !q->peer_o[p] || !q->peer_ctrl[p]) {
+            return fu::fail(FU_E_ARG, "fu_pull_outproj: bad shard or missing buffer for rank %d", p);
+        }
+        heads_seen += q->head_splits[p];
+    }
+    if (heads_seen < 1 || heads_seen > MAX_HEADS) {
+        return fu::fail(FU_E_ARG, "fu_pull_outproj: %d heads (need 1..%d)", heads_seen, MAX_HEADS);
+    }
+    // The puller warps read row (batch, seq_off + s) of rank p's buffer at
+    // ((batch * s_total + seq_off + s) * head_splits[p]) * 256 bytes, head_splits[p] * 256 bytes long.
+    if (q->seq_off < 0 || q->s_total <= 0 || q->seq_off + q->s_local > q->s_total) {
+        return fu::fail(FU_E_ARG, "fu_pull_outproj: rows %lld..%lld do not lie inside a sequence of %lld",
+                        (long long)q->seq_off, (long long)(q->seq_off + q->s_local), (long long)q->s_total);
+    }
+    const int64_t batches = q->m / q->s_local;
+    for (int p = 0; p < q->world; ++p) {
+        const int64_t last = ((batches - 1) * q->s_total + q->seq_off + q->s_local) * q->head_splits[p] * 256;
+        if (last > q->o_bytes) {
+            return fu::fail(FU_E_ARG, "fu_pull_outproj: the loads from rank %d reach byte %lld of buffers of %lld bytes", p,
+                            (long long)last, (long long)q->o_bytes);
+        }
+    }
+    if (q->m * heads_seen * 256 > q->gather_bytes) {
+        return fu::fail(FU_E_ARG, "fu_pull_outproj: the gathered operand needs %lld bytes, `gather` holds %lld",
+                        (long long)(q->m * heads_seen * 256), (long long)q->gather_bytes);
+    }
+    if (((q->m + BM - 1) / BM) * q->world > q->ready_words) {
+        return fu::fail(FU_E_ARG, "fu_pull_outproj: %lld flags needed, `ready` holds %lld",
+                        (long long)(((q->m + BM - 1) / BM) * q->world), (long long)q->ready_words);
+    }
+    return FU_OK;
+}
+
+extern "C" int fu_pull_outproj(const FuPullArgs* q, void* stream_v)
+{
+    int rc = fu_pull_outproj_check(q);
+    if (rc != FU_OK) {
+        return rc;
     }
     PullArgs a{};
     PullParams& e = a.pull;
@@ -644,7 +723,7 @@ extern "C" int fu_pull_outproj(const FuPullArgs* q, void* stream_v)
         e.peers.ctrl[p] = q->peer_ctrl[p];
     }
     const int64_t k = static_cast<int64_t>(heads) * HEAD_DIM;
-    int rc = fill_core(a.core, q->gather, q->w, q->m, q->n, k, k, q->ldw, q->err);
+    rc = fill_core(a.core, q->gather, q->w, q->m, q->n, k, k, q->ldw, q->err);
     if (rc != FU_OK) {
         return rc;
     }

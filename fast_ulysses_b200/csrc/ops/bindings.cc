@@ -192,7 +192,13 @@ void run_prepared(Group& g, Prepared& p, cudaStream_t stream, int extra_flags)
         return;
     }
     const int64_t out_bytes = nbytes_of(p.plan->out_shape, p.x.scalar_type());
-    g.launch(*p.plan, p.x.data_ptr(), *p.window, p.out_is_window ? nullptr : p.output.data_ptr(),
+    const int64_t elem      = static_cast<int64_t>(p.x.element_size());
+    // one past the last byte of the (possibly strided) input: what the routes may read
+    const int64_t src_bytes = p.x.numel() == 0 ? 0
+                                               : ((p.x.size(0) - 1) * p.x.stride(0) + (p.x.size(1) - 1) * p.x.stride(1)
+                                                  + (p.x.size(2) - 1) * p.x.stride(2) + p.x.size(3))
+                                                     * elem;
+    g.launch(*p.plan, p.x.data_ptr(), src_bytes, *p.window, p.out_is_window ? nullptr : p.output.data_ptr(),
              p.out_is_window ? 0 : out_bytes, stream, extra_flags, p.pool_slot);
 }
 

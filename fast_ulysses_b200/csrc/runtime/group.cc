@@ -394,11 +394,14 @@ void Group::prune_owned()
     }
 }
 
-void Group::launch(const Plan& plan, const void* src, const Window& w, void* out, int64_t out_bytes, void* stream,
-                   int extra_flags, int pool_slot)
+void Group::launch(const Plan& plan, const void* src, int64_t src_bytes, const Window& w, void* out,
+                   int64_t out_bytes, void* stream, int extra_flags, int pool_slot)
 {
     FuA2AArgs a{};
-    a.src = src;
+    a.src        = src;
+    a.src_bytes  = src_bytes;
+    a.win_bytes  = w.capacity;
+    a.pool_bytes = pool_capacity_;
     // Every rank passes the whole pool, whatever it chose itself: a peer may have chosen any buffer.
     a.n_pool  = static_cast<int32_t>(pool_.size());
     a.my_slot = pool_slot;

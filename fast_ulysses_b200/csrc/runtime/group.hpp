@@ -98,9 +98,11 @@ public:
     // Typed view of a window's dense prefix.
     static at::Tensor view_of(const Window& w, at::IntArrayRef shape, at::ScalarType dtype);
 
-    // Launch on `stream`. `out` may be null (result stays in the window).
-    void launch(const Plan& plan, const void* src, const Window& w, void* out, int64_t out_bytes, void* stream,
-                int extra_flags, int pool_slot = 0);
+    // Launch on `stream`. `out` may be null (result stays in the window). `src_bytes` is the extent
+    // of the input behind `src`; with the capacities of the window and the pool it lets the launcher
+    // refuse a route that would leave its buffer.
+    void launch(const Plan& plan, const void* src, int64_t src_bytes, const Window& w, void* out, int64_t out_bytes,
+                void* stream, int extra_flags, int pool_slot = 0);
     void barrier(Role role, void* stream);
 
     // CPU/gloo execution of the same plan.

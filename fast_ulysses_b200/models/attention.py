@@ -58,6 +58,10 @@ class _SPAttention(torch.autograd.Function):
             x2 = x2.contiguous()
         N = mod.heads
         need_grad = any(ctx.needs_input_grad[:6])
+        # q, k, v and the attention output live in the module's symmetric buffers, not in tensors
+        # saved for backward: a second forward overwrites them. Number the forwards so that a
+        # backward which would read another call's activations refuses instead.
+        mod._forward_count += 1
         y_save = torch.empty(m, 2 * N * HEAD_DIM, dtype=torch.bfloat16, device=x.device) if need_grad else None
         mod._launch_scatter(x2, w_qkv, mod.qkv_win, 3, 2, gamma_q, gamma_k, y_save)
         q, k, v = mod.q_view, mod.k_view, mod.v_view
@@ -67,10 +71,12 @@ class _SPAttention(torch.autograd.Function):
         ready = mod._ready_flags(m)
         outproj.pull_outproj_raw(w_o, out, gather, ready, s_local=s_local, seq_off=mod.seq_off, s_total=mod.s_total,
                                  head_splits=mod.head_splits, rank=mod.rank, peer_o=mod.o_buf.base, ctrl=mod.o_buf.ctrl,
-                                 bias=b_o.float() if b_o is not None else None, timeout_ms=mod.timeout_ms)
+                                 o_bytes=mod._region,
+                                 bias=mod._f32("b_o", b_o) if b_o is not None else None, timeout_ms=mod.timeout_ms)
         if need_grad:
             ctx.save_for_backward(x2, w_qkv, gamma_q, gamma_k, w_o, y_save, gather, lse)
             ctx.mod = mod
+            ctx.forward_id = mod._forward_count
             ctx.has_bias = b_o is not None
             ctx.x_shape = x.shape
         return out.view(b, s_local, hidden)
@@ -79,6 +85,13 @@ class _SPAttention(torch.autograd.Function):
     def backward(ctx, dy):
         x2, w_qkv, gamma_q, gamma_k, w_o, y_save, gather, lse = ctx.saved_tensors
         mod = ctx.mod
+        if ctx.forward_id != mod._forward_count:
+            raise RuntimeError(
+                "UlyssesSelfAttention: forward ran again on this module before this backward; q, k, v and the "
+                "attention output live in the module's symmetric buffers and now belong to the later call "
+                f"(this backward is for forward #{ctx.forward_id}, the buffers hold #{mod._forward_count}). Run "
+                "backward before the next forward (gradient accumulation: forward, backward, forward, backward), "
+                "use one module per activation that must stay alive, or recompute the forward.")
         b, s_local, hidden = ctx.x_shape
         m, N = b * s_local, mod.heads
         dy2 = dy.reshape(m, hidden)
@@ -158,6 +171,17 @@ class UlyssesSelfAttention(nn.Module):
         self.o_view = self.o_buf.view(0, shape)
         self.do_view = self.do_win.view(0, shape)
         self._ready = None
+        self._forward_count = 0
+        self._f32_cache: dict[str, tuple[int, torch.Tensor]] = {}
+
+    def _f32(self, name: str, param: torch.Tensor) -> torch.Tensor:
+        """fp32 copy of a small parameter, remade only when the parameter has changed in place."""
+        hit = self._f32_cache.get(name)
+        key = (param._version, param.data_ptr())
+        if hit is None or hit[0] != key:
+            hit = (key, param.detach().float().contiguous())
+            self._f32_cache[name] = hit
+        return hit[1]
 
     def _ready_flags(self, m: int) -> torch.Tensor:
         n = ((m + 127) // 128) * self.world
@@ -176,9 +200,8 @@ class UlyssesSelfAttention(nn.Module):
         a.eps = self.eps
         a.rank, a.world = self.rank, self.world
         if n_normed:
-            self._gq32 = gamma_q.detach().float().contiguous()
-            self._gk32 = gamma_k.detach().float().contiguous()
-            a.rope, a.gamma_q, a.gamma_k = self.rope.data_ptr(), self._gq32.data_ptr(), self._gk32.data_ptr()
+            gq32, gk32 = self._f32("gamma_q", gamma_q), self._f32("gamma_k", gamma_k)
+            a.rope, a.gamma_q, a.gamma_k = self.rope.data_ptr(), gq32.data_ptr(), gk32.data_ptr()
         for p in range(self.world):
             a.head_splits[p] = self.head_splits[p]
             a.win_q[p] = win.base[p]
@@ -188,6 +211,7 @@ class UlyssesSelfAttention(nn.Module):
         a.timeout_ms = self.timeout_ms
         a.err = gemm.error_word(x2.device).data_ptr()
         a.n_types, a.n_normed = n_types, n_normed
+        a.win_bytes = self._region
         if y_save is not None:
             a.y_save, a.ld_y = y_save.data_ptr(), y_save.stride(0)
         assert w.shape[0] == n_types * self.heads * HEAD_DIM and x2.dtype == torch.bfloat16

@@ -35,7 +35,8 @@ class FuA2AArgs(C.Structure):
                 ("ctas", C.c_int32), ("timeout_ms", C.c_uint32), ("routes", FuRoute * FU_MAX_WORLD),
                 ("own_direct", C.c_int32), ("n_out_routes", C.c_int32), ("out_routes", FuRoute * 2),
                 ("peer_pool", (C.c_void_p * FU_POOL_SLOTS) * FU_MAX_WORLD), ("n_pool", C.c_int32),
-                ("my_slot", C.c_int32), ("peer_slot", C.c_int8 * FU_MAX_WORLD)]
+                ("my_slot", C.c_int32), ("peer_slot", C.c_int8 * FU_MAX_WORLD), ("win_bytes", C.c_int64),
+                ("pool_bytes", C.c_int64), ("src_bytes", C.c_int64)]
 
 
 _lib = None
@@ -59,6 +60,9 @@ def lib() -> C.CDLL:
                      "fu_qk_norm_rope_bwd"):
             getattr(_lib, name).restype = C.c_int
             getattr(_lib, name).argtypes = [C.c_void_p, C.c_void_p]
+        for name in ("fu_a2a4d_check", "fu_qkv_rope_scatter_check", "fu_pull_outproj_check"):
+            getattr(_lib, name).restype = C.c_int
+            getattr(_lib, name).argtypes = [C.c_void_p]
     return _lib
 
 
@@ -89,7 +93,7 @@ class FuQkvArgs(C.Structure):
                 ("win_k", C.c_void_p * FU_MAX_WORLD), ("win_v", C.c_void_p * FU_MAX_WORLD),
                 ("peer_ctrl", C.c_void_p * FU_MAX_WORLD), ("flags", C.c_int32), ("timeout_ms", C.c_uint32),
                 ("ctas", C.c_int32), ("err", C.c_void_p), ("n_types", C.c_int32), ("n_normed", C.c_int32),
-                ("y_save", C.c_void_p), ("ld_y", C.c_int64)]
+                ("y_save", C.c_void_p), ("ld_y", C.c_int64), ("win_bytes", C.c_int64)]
 
 
 def stream_ptr():
@@ -118,7 +122,7 @@ class FuPullArgs(C.Structure):
                 ("head_splits", C.c_int32 * FU_MAX_WORLD), ("peer_o", C.c_void_p * FU_MAX_WORLD),
                 ("peer_ctrl", C.c_void_p * FU_MAX_WORLD), ("gather", C.c_void_p), ("ready", C.c_void_p),
                 ("flags", C.c_int32), ("timeout_ms", C.c_uint32), ("ctas", C.c_int32), ("pad_", C.c_int32),
-                ("err", C.c_void_p)]
+                ("err", C.c_void_p), ("o_bytes", C.c_int64), ("gather_bytes", C.c_int64), ("ready_words", C.c_int64)]
 
 
 class FuNormRopeBwdArgs(C.Structure):

@@ -32,8 +32,7 @@ def _fill(a, q, k, v, o):
 
 
 def fmha_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scale: float | None = None,
-             out: torch.Tensor | None = None, ctas: int = 0, poly: int | None = None,
-             trace: torch.Tensor | None = None):
+             out: torch.Tensor | None = None, ctas: int = 0, poly: int | None = None):
     """``softmax(q k^T * scale) v`` for (b, s, h, 128) bf16 tensors. Returns ``(o, lse)`` with
     ``lse`` of shape (b, h, s_q), fp32, natural log. ``poly`` (0, 2, 4 or 6) overrides how many of
     every 16 exponential pairs are computed on the FMA pipe instead of the special-function unit."""
@@ -48,8 +47,6 @@ def fmha_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scale: float 
     a.ctas = ctas
     if poly is not None:
         a.flags = 0x1000 | ((poly & 15) << 8)  # FU_FMHA_POLY(poly)
-    if trace is not None:  # int64[256] on the device: SM clock of 32 pipeline events for 8 kv steps of CTA 0
-        a.trace = trace.data_ptr()
     ck.check(ck.lib().fu_fmha_fwd(C.byref(a), ck.stream_ptr()))
     return o, lse
 

@@ -20,10 +20,11 @@ HEAD_DIM = 128
 def qkv_rope_scatter_raw(x: torch.Tensor, w: torch.Tensor, rope: torch.Tensor, gamma_q: torch.Tensor,
                          gamma_k: torch.Tensor, *, heads: int, s_local: int, seq_off: int, s_total: int,
                          head_splits: list[int], rank: int, win_q: list[int], win_k: list[int], win_v: list[int],
-                         ctrl: list[int], eps: float = 1e-6, flags: int = 0, timeout_ms: int = 10000,
-                         ctas: int = 0) -> None:
+                         ctrl: list[int], win_bytes: int, eps: float = 1e-6, flags: int = 0,
+                         timeout_ms: int = 10000, ctas: int = 0) -> None:
     """x: (b * s_local, hidden) bf16, w: (3 * heads * 128, hidden) bf16 (rows: q heads, k heads,
-    v heads). Each rank's q/k/v window has layout (b, s_total, head_splits[p], 128) bf16."""
+    v heads). Each rank's q/k/v window has layout (b, s_total, head_splits[p], 128) bf16 and
+    ``win_bytes`` bytes behind its base; the launcher refuses a shape whose stores would leave it."""
     assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.stride(1) == 1 and w.stride(1) == 1
     assert w.shape[0] == 3 * heads * HEAD_DIM and w.shape[1] == x.shape[1]
     assert rope.dtype == torch.float32 and rope.shape == (s_local, HEAD_DIM // 2, 2) and rope.is_contiguous()
@@ -41,6 +42,7 @@ def qkv_rope_scatter_raw(x: torch.Tensor, w: torch.Tensor, rope: torch.Tensor, g
         a.head_splits[p] = head_splits[p]
         a.win_q[p], a.win_k[p], a.win_v[p], a.peer_ctrl[p] = win_q[p], win_k[p], win_v[p], ctrl[p]
     a.flags, a.timeout_ms, a.ctas = flags, timeout_ms, ctas
+    a.win_bytes = win_bytes
     a.err = error_word(x.device).data_ptr()
     ck.check(ck.lib().fu_qkv_rope_scatter(C.byref(a), ck.stream_ptr()))
 

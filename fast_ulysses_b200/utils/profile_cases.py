@@ -76,7 +76,8 @@ def case_qkv():
                                  rank=0, win_q=[t.data_ptr() for t in wins],
                                  win_k=[t.data_ptr() + region for t in wins],
                                  win_v=[t.data_ptr() + 2 * region for t in wins],
-                                 ctrl=[t.data_ptr() + 3 * region for t in wins], flags=ck.FU_A2A_NO_HANDSHAKE)
+                                 ctrl=[t.data_ptr() + 3 * region for t in wins], win_bytes=region,
+                                 flags=ck.FU_A2A_NO_HANDSHAKE)
 
     ms = _time(run)
     print(f"fused qkv+rmsnorm+rope+scatter 9450x15360x5120: {ms:.4f} ms, {2 * 9450 * 15360 * 5120 / ms / 1e9:.0f} TFLOP/s")
@@ -98,7 +99,7 @@ def case_outproj():
     def run():
         outproj.pull_outproj_raw(w, out, gather, ready, s_local=m, seq_off=0, s_total=S, head_splits=hs, rank=0,
                                  peer_o=[t.data_ptr() for t in o_bufs], ctrl=[t.data_ptr() for t in ctrls],
-                                 flags=ck.FU_A2A_NO_HANDSHAKE)
+                                 o_bytes=o_bufs[0].numel() * 2, flags=ck.FU_A2A_NO_HANDSHAKE)
 
     ms = _time(run)
     print(f"pull + out-proj 9450x5120x5120: {ms:.4f} ms, {2 * 9450 * 5120 * 5120 / ms / 1e9:.0f} TFLOP/s")

@@ -54,6 +54,7 @@ def emulate(b, seq, heads, d, mode, dtype, flags, copy_out, ctas=0, own_direct=T
                 a.peer_win[p] = wins[p].data_ptr()
                 a.peer_ctrl[p] = wins[p].data_ptr() + wbytes
             a.rank, a.world = r, ws
+            a.win_bytes, a.src_bytes = wbytes, inputs[r].numel() * elem
             a.flags = flags | ck.FU_A2A_NO_HANDSHAKE
             a.ctas = ctas
             rows = plans[r][2].tolist()
@@ -197,6 +198,7 @@ def test_pool_buffers_chosen_rank_by_rank(flags, mode):
                 a.peer_pool[p][k] = pools[p][k].data_ptr()
         a.n_pool, a.my_slot = 2, slots[r]
         a.rank, a.world = r, ws
+        a.win_bytes, a.pool_bytes, a.src_bytes = wbytes, wbytes, inputs[r].numel() * elem
         a.flags = flags | ck.FU_A2A_NO_HANDSHAKE
         rows = plans[r][2].tolist()
         a.n_routes = len(rows)
@@ -316,6 +318,7 @@ def test_wait_runs_out_and_reports():
         a.peer_win[p] = wins[p].data_ptr()
         a.peer_ctrl[p] = wins[p].data_ptr() + wbytes
     a.rank, a.world, a.timeout_ms = 0, ws, 200
+    a.win_bytes, a.src_bytes = wbytes, x.numel() * elem
     rows = plans[2].tolist()
     a.n_routes = len(rows)
     for i, row in enumerate(rows):

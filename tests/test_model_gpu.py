@@ -59,3 +59,27 @@ def test_dit_stack_single_rank():
     assert rel_err(y, yr) < 3e-2, rel_err(y, yr)
     assert rel_err(x.grad, xr.grad) < 6e-2, rel_err(x.grad, xr.grad)
     g.destroy()
+
+
+def test_backward_after_a_later_forward_is_refused():
+    """The block keeps q, k, v and the attention output in its symmetric buffers: a backward for a
+    forward that a later forward has overwritten must raise, not return another call's gradients."""
+    torch.manual_seed(2)
+    g = fu.UlyssesGroup(device="cuda")
+    grid, hidden, heads = (2, 8, 16), 256, 2
+    attn = UlyssesSelfAttention(g, hidden, heads, grid=grid)
+    x1 = torch.randn(1, 256, hidden, device="cuda").bfloat16().requires_grad_()
+    x2 = torch.randn(1, 256, hidden, device="cuda").bfloat16().requires_grad_()
+    y1 = attn(x1)
+    y2 = attn(x2)
+    with pytest.raises(RuntimeError, match="forward ran again"):
+        y1.sum().backward()
+    y2.sum().backward()  # the latest forward still owns the buffers
+    # forward, backward, forward, backward (gradient accumulation) is the supported order
+    attn.zero_grad()
+    attn(x1).sum().backward()
+    first = attn.w_o.grad.clone()
+    attn(x1).sum().backward()
+    assert torch.allclose(attn.w_o.grad.float(), 2 * first.float(), rtol=2e-2, atol=1e-3)
+    gemm.check_errors()
+    g.destroy()

@@ -28,7 +28,8 @@ def run_world(seq, head_splits, n_out, b=1, ctas=0):
         ready = torch.zeros(((m + 127) // 128) * world, dtype=torch.int32, device="cuda")
         outproj.pull_outproj_raw(w, out, gather, ready, s_local=seq[r], seq_off=s0, s_total=S,
                                  head_splits=head_splits, rank=r, peer_o=[t.data_ptr() for t in o_bufs],
-                                 ctrl=[t.data_ptr() for t in ctrls], bias=bias, residual=res,
+                                 ctrl=[t.data_ptr() for t in ctrls], o_bytes=b * S * max(head_splits) * 256,
+                                 bias=bias, residual=res,
                                  flags=ck.FU_A2A_NO_HANDSHAKE, ctas=ctas)
         torch.cuda.synchronize()
         gemm.check_errors()

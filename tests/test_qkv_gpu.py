@@ -32,7 +32,7 @@ def run_world(seq, head_splits, hidden, b=1, grid=(4, 6, 10)):
             x, w, rope, gq, gk, heads=heads, s_local=seq[r], seq_off=s0, s_total=S, head_splits=head_splits, rank=r,
             win_q=[t.data_ptr() for t in wins], win_k=[t.data_ptr() + region for t in wins],
             win_v=[t.data_ptr() + 2 * region for t in wins], ctrl=[t.data_ptr() + 3 * region for t in wins],
-            flags=ck.FU_A2A_NO_HANDSHAKE)
+            win_bytes=region, flags=ck.FU_A2A_NO_HANDSHAKE)
         refs.append(qkv.qkv_reference(x, w, rope, gq, gk, heads))
         xs.append(x)
         s0 += seq[r]
