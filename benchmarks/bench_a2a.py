@@ -1,10 +1,15 @@
 """Detailed all-to-all benchmarks (the headline number lives in the repository's bench.py).
 
     torchrun --nproc-per-node N --master-addr 127.0.0.1 benchmarks/bench_a2a.py --mode stages
-    modes: stages | zerocopy | padding | sweep | overlap | fp8
+    modes: stages | zerocopy | padding | sweep | overlap | fp8 | link
 
-Modes follow the reference's benchmark/bench_a2a.py:168-399 (stages, zerocopy, padding, sweep,
-overlap); its `link` and `zerosm` modes measured the copy engines, which this library does not use.
+Modes follow the reference's benchmark/bench_a2a.py:168-443 (stages, zerocopy, padding, sweep,
+overlap, link). `link` is the ceiling every NVLink fraction in this repository is quoted against:
+flat 64 MiB copies from rank r into rank (r+1) % N's memory through this library's own two data
+paths (bulk copies, and 16-byte loads and stores), one flow and all N flows at once, with no
+handshake and no relayout. `overlap` also reports how much the GEMMs slow down while the exchange
+runs beside them: an exchange on the SMs can hide itself by taking time from them. The reference's
+`zerosm` mode measured its copy engines, which this library does not use.
 BASE is the torch.distributed form (permute, all_to_all_single, permute). Every number is a CUDA
 event time, L2 flushed between iterations, the maximum over ranks; rank 0 prints one JSON line
 per measurement.
@@ -70,7 +75,7 @@ def emit(rank, **kw):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--mode", default="stages", choices=["stages", "zerocopy", "padding", "sweep", "overlap", "fp8"])
+    ap.add_argument("--mode", default="stages", choices=["stages", "zerocopy", "padding", "sweep", "overlap", "fp8", "link"])
     ap.add_argument("--shape", default="wan-720p", choices=list(SHAPES))
     ap.add_argument("--iters", type=int, default=25)
     args = ap.parse_args()
@@ -122,10 +127,30 @@ def main():
             gemms()
             h.wait()
 
+        # how long the GEMMs themselves take while the exchange runs beside them (events around the
+        # GEMMs only, on the caller's stream)
+        def gemms_beside():
+            h = g.all_to_all_4d_async(x)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            gemms()
+            e1.record()
+            h.wait()
+            return e0, e1
+
         t_g, t_a = run(gemms, args.iters), run(lambda: g.all_to_all_4d(x), args.iters)
         t_s, t_c = run(serial, args.iters), run(concurrent, args.iters)
+        pairs = []
+        for _ in range(args.iters):
+            flush.zero_()
+            pairs.append(gemms_beside())
+        torch.cuda.synchronize()
+        beside = sorted(a.elapsed_time(b) for a, b in pairs)[len(pairs) // 2]
+        tb = torch.tensor([beside], device="cuda", dtype=torch.float64)
+        dist.all_reduce(tb, op=dist.ReduceOp.MAX)
         emit(rank, mode="overlap", shape=args.shape, world=world, gemm_ms=t_g, a2a_ms=t_a, serial_ms=t_s,
-             concurrent_ms=t_c, hidden_pct=100.0 * (t_s - t_c) / t_a)
+             concurrent_ms=t_c, hidden_pct=100.0 * (t_s - t_c) / t_a, gemm_beside_exchange_ms=float(tb),
+             gemm_slowdown_pct=100.0 * (float(tb) - t_g) / t_g)
     elif args.mode == "fp8":
         from fast_ulysses_b200.ops import fp8
 
@@ -135,6 +160,39 @@ def main():
         emit(rank, mode="fp8", world=world, bf16_ms=run(lambda: g.all_to_all_4d(x128), args.iters),
              fp8_block_scaled_ms=run(lambda: fp8.all_to_all_4d_fp8(g, x128), args.iters),
              int8_payload_ms=run(lambda: g.all_to_all_4d(x8), args.iters))
+    elif args.mode == "link":
+        import ctypes as C
+
+        from fast_ulysses_b200.ops import _ckernels as ck
+
+        nbytes = 64 << 20
+        buf = g._handle.symm_alloc(nbytes)  # collective: every rank's buffer, mapped on every rank
+        ptrs = g._handle.symm_ptrs(buf)
+        bases, ctrls = ptrs[:world], ptrs[world:]
+        src = torch.full((nbytes,), 1, dtype=torch.uint8, device="cuda")
+        peer = (rank + 1) % world
+
+        def flat(flags):
+            a = ck.FuA2AArgs()
+            a.src = src.data_ptr()
+            for p in range(world):
+                a.peer_win[p], a.peer_ctrl[p] = bases[p], ctrls[p]
+            a.rank, a.world, a.n_routes = rank, world, 1
+            a.routes[0] = ck.FuRoute(peer, 0, 0, 0, nbytes, nbytes, nbytes, 1, 1, 0, 0)
+            a.flags = ck.FU_A2A_NO_HANDSHAKE | flags
+            a.win_bytes, a.src_bytes = nbytes, nbytes
+            ck.check(ck.lib().fu_a2a4d(C.byref(a), ck.stream_ptr()))
+
+        for name, flags in (("bulk", 0), ("ldst", ck.FU_A2A_LDST)):
+            if world == 1:
+                emit(rank, mode="link", path=name, note="world_size 1: no link to measure")
+                continue
+            one = run(lambda: flat(flags) if rank == 0 else None, args.iters)  # a single flow on the fabric
+            every = run(lambda: flat(flags), args.iters)                      # one flow per rank
+            emit(rank, mode="link", path=name, world=world, bytes=nbytes, one_flow_ms=one,
+                 one_flow_gb_per_s=nbytes / one / 1e6, all_flows_ms=every, per_flow_gb_per_s=nbytes / every / 1e6,
+                 aggregate_gb_per_s=world * nbytes / every / 1e6)
+        del buf
     g.check()
     g.destroy()
     dist.destroy_process_group()

@@ -15,7 +15,7 @@ import subprocess
 import sys
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-MODES = ["stages", "zerocopy", "padding", "sweep", "overlap", "fp8"]
+MODES = ["link", "stages", "zerocopy", "padding", "sweep", "overlap", "fp8"]
 
 
 def sh(cmd: list[str]) -> str:

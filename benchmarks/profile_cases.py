@@ -2,7 +2,7 @@
 L2 so that DRAM counters mean something, a few hundred MB on the device, one to three launches of
 the kernel of interest after a short warm-up.
 
-    python -m fast_ulysses_b200.utils.profile_cases a2a|gemm|qkv|outproj|fmha_fwd|fmha_bwd|fmha_bwd_det
+    python benchmarks/profile_cases.py a2a|gemm|qkv|outproj|fmha_fwd|fmha_bwd|fmha_bwd_det
 
 Each case prints the CUDA-event time of its last launch, so the same command is also a quick
 timing check when run without a profiler.
@@ -10,9 +10,12 @@ timing check when run without a profiler.
 
 from __future__ import annotations
 
+import os
 import sys
 
 import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 
 def _time(fn, warm=2, reps=2):
@@ -143,7 +146,7 @@ CASES = {"a2a": case_a2a, "gemm": case_gemm, "qkv": case_qkv, "outproj": case_ou
 if __name__ == "__main__":
     name = sys.argv[1] if len(sys.argv) > 1 else ""
     if name not in CASES:
-        sys.exit(f"usage: python -m fast_ulysses_b200.utils.profile_cases {'|'.join(CASES)}")
+        sys.exit(f"usage: python benchmarks/profile_cases.py {'|'.join(CASES)}")
     CASES[name]()
     from fast_ulysses_b200.ops import gemm as _g
 

@@ -16,6 +16,7 @@
 // announcement (FuCtrl::slot_of) and every sender shifts its routes to that rank accordingly, so
 // ranks with different numbers of live results need not agree on anything.
 #include "fu_kernels.h"
+#include "handshake.cuh"
 #include "host_util.h"
 #include "ptx.cuh"
 
@@ -65,10 +66,8 @@ struct RouteSet {
 struct KArgs {
     RouteSet push;
     RouteSet copy_out;  // n == 0 when there is no fused copy-out
-    FuCtrl*  own;
-    FuCtrl*  peer_ctrl[FU_MAX_WORLD];
-    int      rank, world, flags;
-    uint64_t timeout_ns;
+    fu::Peers peers;  // control blocks, rank, world size, time limit of every cross-rank wait
+    int       flags;
     // Output pool: `dst` of a route to rank p is built for p's window; if p announces pool buffer
     // k for this call, the route is shifted by pool_delta[p][k - 1] = buffer - window.
     int64_t  pool_delta[FU_MAX_WORLD][FU_POOL_SLOTS];
@@ -143,57 +142,6 @@ struct ChunkCursor {
     }
 };
 
-__device__ void report(FuCtrl* own, uint32_t code, uint32_t peer, uint64_t expected, uint64_t seen)
-{
-    if (atomicCAS(&own->status[0], 0u, code) == 0u) {
-        own->status[1] = peer;
-        own->status[2] = static_cast<uint32_t>(expected);
-        own->status[3] = static_cast<uint32_t>(expected >> 32);
-        own->status[4] = static_cast<uint32_t>(seen);
-        own->status[5] = static_cast<uint32_t>(seen >> 32);
-    }
-}
-
-// Called by one full warp. Lane p < world announces `value` to rank p.
-__device__ void announce(const KArgs& a, uint64_t value, bool with_slot = false)
-{
-    const int lane = threadIdx.x & 31;
-    if (lane < a.world && !(a.flags & FU_A2A_MUTE)) {
-        if (with_slot) {
-            // where this rank wants the payload of this call; ordered before the announcement by
-            // the release below (same thread, same destination rank)
-            *reinterpret_cast<volatile uint8_t*>(&a.peer_ctrl[lane]->slot_of[a.rank]) = static_cast<uint8_t>(a.my_slot);
-        }
-        red_release_sys_max(&a.peer_ctrl[lane]->flags[a.rank], value);
-    }
-}
-
-// Called by one full warp. Lane p < world waits until rank p has announced at least `target`,
-// for the ranks named in `who` (bit p). Returns false (on every lane) after the time limit, having
-// recorded who was missing.
-__device__ bool await(const KArgs& a, uint64_t target, uint32_t code, uint32_t who = 0xffffffffu)
-{
-    const int lane = threadIdx.x & 31;
-    bool      ok   = true;
-    if (lane < a.world && ((who >> lane) & 1u)) {
-        const uint64_t t0    = globaltimer_ns();
-        uint32_t       spins = 0;
-        uint64_t       seen;
-        while ((seen = ld_acquire_sys(&a.own->flags[lane])) < target) {
-            ++spins;
-            if ((spins & 63u) == 0u) {
-                if (globaltimer_ns() - t0 > a.timeout_ns || spins > 0x7fffff00u) {
-                    report(a.own, code, static_cast<uint32_t>(lane), target, seen);
-                    ok = false;
-                    break;
-                }
-                __nanosleep(64);
-            }
-        }
-    }
-    return __all_sync(0xffffffffu, ok);
-}
-
 // ---- data movers ------------------------------------------------------------------------------------
 struct BulkPipe {
     uint8_t*  stage[kStages];
@@ -266,7 +214,7 @@ __device__ bool bulk_move(const RouteSet& set, const BulkPipe& p, int64_t& jbase
         const int      s      = static_cast<int>(js % kStages);
         const uint32_t parity = static_cast<uint32_t>((js / kStages) & 1);
         if (!mbar_wait(&p.full[s], parity)) {
-            report(own, FU_ST_COPY_TIMEOUT, 0, static_cast<uint64_t>(js), 0);
+            fu::hs_report(own, FU_ST_COPY_TIMEOUT, 0, static_cast<uint64_t>(js), 0);
             ok = false;
         }
         ok = __all_sync(0xffffffffu, ok);
@@ -330,7 +278,7 @@ __global__ void __launch_bounds__(kBulk ? 32 : kLdstThreads, kBulk ? 1 : kLdstCt
     const int  warp      = threadIdx.x >> 5;
     const bool handshake = !(a.flags & FU_A2A_NO_HANDSHAKE);
     const bool stamps    = (a.flags & FU_A2A_STAMPS) && blockIdx.x == 0 && threadIdx.x == 0;
-    FuCtrl*    own       = a.own;
+    FuCtrl*    own       = a.peers.own;
 
     BulkPipe pipe;
     if (kBulk) {
@@ -369,19 +317,19 @@ __global__ void __launch_bounds__(kBulk ? 32 : kLdstThreads, kBulk ? 1 : kLdstCt
     bool alive = true;
     if (handshake && warp == 0) {
         if (blockIdx.x == 0) {
-            announce(a, base + 1, true);
+            fu::hs_announce(a.peers, base + 1, a.my_slot);
             if (a.flags & FU_A2A_EARLY_PUBLISH) {
-                announce(a, base + 2);
+                fu::hs_announce(a.peers, base + 2);
             }
         }
-        alive = await(a, base + 1, FU_ST_OPEN_TIMEOUT, who);
+        alive = fu::hs_await(a.peers, base + 1, FU_ST_OPEN_TIMEOUT, who);
     }
     if (warp == 0) {
         // Which buffer each rank wants this call's payload in: announced with the opening flag
         // (the acquire in await() orders this read, so only the ranks waited for are read), or
         // given by the host when there is no handshake.
         const int lane = threadIdx.x & 31;
-        if (lane < a.world && ((who >> lane) & 1u)) {
+        if (lane < a.peers.world && ((who >> lane) & 1u)) {
             int slot = handshake ? static_cast<int>(*reinterpret_cast<volatile uint8_t*>(&own->slot_of[lane]))
                                  : static_cast<int>(a.peer_slot[lane]);
             if (slot < 0 || slot > a.n_pool) {
@@ -431,10 +379,10 @@ __global__ void __launch_bounds__(kBulk ? 32 : kLdstThreads, kBulk ? 1 : kLdstCt
     if (handshake && warp == 0) {
         if (last_in) {
             fence_sys();
-            announce(a, base + 2);
+            fu::hs_announce(a.peers, base + 2);
         }
         if (last_in || copying) {
-            await(a, base + 2, FU_ST_CLOSE_TIMEOUT);
+            fu::hs_await(a.peers, base + 2, FU_ST_CLOSE_TIMEOUT);
         }
     }
     if (stamps) {
@@ -473,8 +421,8 @@ __global__ void __launch_bounds__(32, 1)
     barrier_kernel(FuCtrl* own, const __grid_constant__ KArgs a)
 {
     const uint64_t base = *reinterpret_cast<volatile uint64_t*>(&own->epoch);
-    announce(a, base + 1);
-    await(a, base + 1, FU_ST_OPEN_TIMEOUT);
+    fu::hs_announce(a.peers, base + 1);
+    fu::hs_await(a.peers, base + 1, FU_ST_OPEN_TIMEOUT);
     __syncwarp();
     if (threadIdx.x == 0) {
         *reinterpret_cast<volatile uint64_t*>(&own->epoch) = base + 1;
@@ -589,17 +537,18 @@ int build_args(const FuA2AArgs* args, KArgs& k)
     if (in.n_routes < 0 || in.n_routes > FU_MAX_WORLD) {
         return fu::fail(FU_E_ARG, "fu_a2a4d: %d routes", in.n_routes);
     }
-    k.rank       = in.rank;
-    k.world      = in.world;
-    k.flags      = in.flags;
-    k.timeout_ns = static_cast<uint64_t>(in.timeout_ms ? in.timeout_ms : kDefaultTimeoutMs) * 1000000ull;
+    k.peers.rank       = in.rank;
+    k.peers.world      = in.world;
+    k.peers.mute       = (in.flags & FU_A2A_MUTE) ? 1 : 0;
+    k.peers.timeout_ns = static_cast<uint64_t>(in.timeout_ms ? in.timeout_ms : kDefaultTimeoutMs) * 1000000ull;
+    k.flags            = in.flags;
     for (int p = 0; p < in.world; ++p) {
         if (!in.peer_win[p] || !in.peer_ctrl[p]) {
             return fu::fail(FU_E_ARG, "fu_a2a4d: no window or control block for rank %d", p);
         }
-        k.peer_ctrl[p] = in.peer_ctrl[p];
+        k.peers.ctrl[p] = in.peer_ctrl[p];
     }
-    k.own = in.peer_ctrl[in.rank];
+    k.peers.own = in.peer_ctrl[in.rank];
     if (in.n_routes > 0 && !aligned16(in.src)) {
         return fu::fail(FU_E_ARG, "fu_a2a4d: the input is not 16-byte aligned");
     }
@@ -804,18 +753,19 @@ extern "C" int fu_barrier(FuCtrl* const* peer_ctrl, int rank, int world, uint32_
         return fu::fail(FU_E_ARG, "fu_barrier: rank %d / world %d out of range", rank, world);
     }
     KArgs k{};
-    k.rank       = rank;
-    k.world      = world;
-    k.flags      = flags;
-    k.timeout_ns = static_cast<uint64_t>(timeout_ms ? timeout_ms : kDefaultTimeoutMs) * 1000000ull;
+    k.peers.rank       = rank;
+    k.peers.world      = world;
+    k.peers.mute       = (flags & FU_A2A_MUTE) ? 1 : 0;
+    k.peers.timeout_ns = static_cast<uint64_t>(timeout_ms ? timeout_ms : kDefaultTimeoutMs) * 1000000ull;
+    k.flags            = flags;
     for (int p = 0; p < world; ++p) {
         if (!peer_ctrl[p]) {
             return fu::fail(FU_E_ARG, "fu_barrier: no control block for rank %d", p);
         }
-        k.peer_ctrl[p] = peer_ctrl[p];
+        k.peers.ctrl[p] = peer_ctrl[p];
     }
-    k.own = peer_ctrl[rank];
-    barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream_v)>>>(k.own, k);
+    k.peers.own = peer_ctrl[rank];
+    barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream_v)>>>(k.peers.own, k);
     FU_CUDA_OK(cudaGetLastError());
     return FU_OK;
 }

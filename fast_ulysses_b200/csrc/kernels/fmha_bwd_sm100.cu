@@ -181,14 +181,29 @@ extern "C" int fu_fmha_bwd_noalloc(const FuFmhaArgs* a, void* stream)
     const size_t sq_pad = (static_cast<size_t>(a->seq_q) + BLK - 1) / BLK * BLK;
     const size_t stats  = 2 * sizeof(float) * a->batch * a->heads * sq_pad;
     const size_t acc    = sizeof(float) * a->batch * static_cast<size_t>(a->seq_q) * a->heads * D;
-    if (stats > kNoAllocStatsBytes || acc > kNoAllocAccBytes) {
+    // Two limits, each named in its own message: the dQ accumulator bounds the number of query rows,
+    // the statistics bound the number of rows AFTER seq_q has been rounded up to 128 per (batch,
+    // head), which is the one that bites for many heads with short sequences.
+    if (acc > kNoAllocAccBytes) {
         return fu::fail(FU_E_ARG,
-                        "fu_fmha_bwd_noalloc: batch %d x heads %d x seq_q %d needs %zu + %zu scratch bytes, the built-in "
-                        "scratch holds %zu + %zu (batch*heads*seq_q <= 16384); use fu_fmha_bwd with your own buffers",
-                        a->batch, a->heads, a->seq_q, stats, acc, kNoAllocStatsBytes, kNoAllocAccBytes);
+                        "fu_fmha_bwd_noalloc: batch %d x heads %d x seq_q %d is %zu query rows; the built-in dQ "
+                        "accumulator holds batch*heads*seq_q <= 16384 rows (%zu bytes). Use fu_fmha_bwd with your own "
+                        "buffers",
+                        a->batch, a->heads, a->seq_q, static_cast<size_t>(a->batch) * a->heads * a->seq_q,
+                        kNoAllocAccBytes);
+    }
+    if (stats > kNoAllocStatsBytes) {
+        return fu::fail(FU_E_ARG,
+                        "fu_fmha_bwd_noalloc: batch %d x heads %d x seq_q %d needs statistics for %zu padded rows; the "
+                        "built-in scratch holds batch*heads*roundup(seq_q, 128) <= 65536 rows (%zu bytes). Use "
+                        "fu_fmha_bwd with your own buffers",
+                        a->batch, a->heads, a->seq_q, static_cast<size_t>(a->batch) * a->heads * sq_pad,
+                        kNoAllocStatsBytes);
     }
     // The array's name is only a host-side handle; the device address has to be asked for, once
-    // per device, with that device current. This happens on the first call on each device.
+    // per device, with that device current. This happens on the first call on each device. The
+    // address is remembered for the life of the process: after cudaDeviceReset() it is stale, and
+    // this entry point must not be used again in that process.
     static void* base[64] = {};
     int          dev      = 0;
     FU_CUDA_OK(cudaGetDevice(&dev));

@@ -118,8 +118,11 @@ FU_API int fu_barrier(FuCtrl* const* peer_ctrl, int rank, int world, uint32_t ti
 
 // ---- tcgen05 GEMMs ------------------------------------------------------------------------------
 // C[m,n] = act(A[m,k] * B[n,k]^T + bias[n]) + residual[m,n]; bf16 operands, fp32 accumulation.
-// act: 0 none, 1 GELU (tanh form), 2 GELU (erf form). `err` (nullable) is a device word that
-// receives a non-zero code if a wait inside the kernel ran out.
+// act: 0 none, 1 GELU (tanh form), 2 GELU (erf form), 3 = multiply by the derivative of the tanh-form
+// GELU at aux[m, n] (the backward of act 1 fused into the dgrad GEMM that produces its incoming
+// gradient). `c_pre` (nullable, leading dimension ldc) additionally receives the value before the
+// activation, which that backward needs. `err` (nullable) is a device word that receives a
+// non-zero code if a wait inside the kernel ran out.
 // flags: an operand may be given with the contraction along its rows instead of its columns
 // (A stored k x m with pitch lda, B stored k x n with pitch ldb). The weight gradient of a linear
 // layer, dW = dY^T X, is then a GEMM over dY and X as they lie in memory.
@@ -135,12 +138,17 @@ typedef struct FuGemmArgs {
     int32_t      ctas;
     uint32_t*    err;
     int32_t      flags;
+    const void*  aux;    // act 3: bf16 (m, n) with leading dimension ldc
+    void*        c_pre;  // bf16 (m, n) with leading dimension ldc, or null
 } FuGemmArgs;
 FU_API int fu_gemm_bf16(const FuGemmArgs* args, void* stream);
 
 // Fused mode-0 path: [q|k|v] = x * W^T (W rows ordered q heads, k heads, v heads; head_dim 128),
 // per-head RMSNorm and RoPE on q and k, each head-row stored into the owning rank's window at
 // (batch, seq_off + s, local head). Windows have layout (b, s_total, head_splits[p], 128) bf16.
+// FuQkvArgs::flags: the weight is given with the contraction along its rows, (k, n) with pitch ldw,
+// and read as it lies in memory (the scatter of d(attention output) = dY W_o uses W_o as stored).
+#define FU_QKV_W_KN 64
 typedef struct FuQkvArgs {
     const void*  x;
     const void*  w;
@@ -158,7 +166,7 @@ typedef struct FuQkvArgs {
     void*        win_k[FU_MAX_WORLD];
     void*        win_v[FU_MAX_WORLD];
     FuCtrl*      peer_ctrl[FU_MAX_WORLD];
-    int32_t      flags;    // FU_A2A_NO_HANDSHAKE, FU_A2A_MUTE
+    int32_t      flags;    // FU_A2A_NO_HANDSHAKE, FU_A2A_MUTE, FU_QKV_W_KN
     uint32_t     timeout_ms;
     int32_t      ctas;
     uint32_t*    err;
@@ -196,6 +204,34 @@ typedef struct FuNormRopeBwdArgs {
     float        eps;
 } FuNormRopeBwdArgs;
 FU_API int fu_qk_norm_rope_bwd(const FuNormRopeBwdArgs* args, void* stream);
+
+// The backward of the fused mode-0 path before its GEMMs: dq, dk and dv are loaded from the ranks
+// that own the heads (each rank's buffers have layout (b, s_total, head_splits[p], 128) bf16 with
+// `src_bytes` bytes behind every base), RoPE and RMSNorm are undone for q and k, and the result is
+// written as d(projection) for q | k | v into `dy` (m, 3 * heads * 128), the A operand of the
+// dgrad and wgrad GEMMs. Replaces a stand-alone mode-1 exchange, fu_qk_norm_rope_bwd and a copy.
+typedef struct FuPullGradsArgs {
+    const void*  peer_dq[FU_MAX_WORLD];
+    const void*  peer_dk[FU_MAX_WORLD];
+    const void*  peer_dv[FU_MAX_WORLD];
+    FuCtrl*      peer_ctrl[FU_MAX_WORLD];
+    int64_t      src_bytes;
+    const void*  y;        // pre-norm q | k saved by fu_qkv_rope_scatter, (m, 2 * heads * 128), leading dim ld_y
+    void*        dy;
+    const float* rope;
+    const float* gamma_q;
+    const float* gamma_k;
+    float*       dgamma_q; // nullable; accumulated into
+    float*       dgamma_k;
+    int64_t      m, s_local, seq_off, s_total, ld_y, ld_dy;
+    int32_t      heads, rank, world;
+    int32_t      head_splits[FU_MAX_WORLD];
+    int32_t      flags;    // FU_A2A_NO_HANDSHAKE, FU_A2A_MUTE
+    uint32_t     timeout_ms;
+    float        eps;
+} FuPullGradsArgs;
+FU_API int fu_pull_qkv_grads(const FuPullGradsArgs* args, void* stream);
+FU_API int fu_pull_qkv_grads_check(const FuPullGradsArgs* args);  // the argument checks alone; no CUDA call
 
 // Fused mode-1 path: C[m, n] = A[m, :] * W[n, :]^T + bias + residual where A is the attention output
 // gathered from its owners: A[m, head*128 + x] = O_owner(head)[batch, seq_off + s, local head, x].
@@ -275,19 +311,51 @@ FU_API int fu_fmha_bwd(const FuFmhaArgs* args, void* stream);
 // cannot afford cudaMalloc's synchronisation). This entry point has no counterpart in the
 // reference. `delta` and `dq_acc` in `args` are ignored: the scratch is a fixed array inside the
 // library (8.5 MiB of every GPU that loads it, held until the process exits). Limits and rules:
-//   * batch * heads * seq_q <= 16384 rows (checked; larger problems are refused with an error);
+//   * two size limits, both checked, a problem beyond either is refused with an error that names it:
+//     batch * heads * seq_q <= 16384 query rows (the dQ accumulator), and
+//     batch * heads * roundup(seq_q, 128) <= 65536 (the softmax statistics are padded to whole
+//     128-row blocks per (batch, head), so many heads with short sequences meet this one first:
+//     1024 (batch, head) pairs of one row each are refused although they are only 1024 rows);
 //   * the first call on each device looks up the array's device address, so make that first call
-//     outside any stream capture;
+//     outside any stream capture; the address is kept for the life of the process and is stale
+//     after cudaDeviceReset();
 //   * all calls share the one array: two calls that overlap on the GPU (different streams, or
 //     different threads) corrupt each other. Calls ordered on one stream are safe, each clears
 //     what it needs to start from zero;
 //   * nothing is allocated or freed: no cudaMalloc/cudaFree, no torch, no library allocator.
 FU_API int fu_fmha_bwd_noalloc(const FuFmhaArgs* args, void* stream);
 
+// ---- LayerNorm without affine parameters (bf16 in and out, fp32 statistics) -------------------------
+// y = (x - mean) * rstd per row; `stats` (rows, 2) fp32 receives (mean, rstd) for the backward.
+FU_API int fu_layernorm_fwd(const void* x, void* y, float* stats, int64_t rows, int64_t cols, int64_t ldx, int64_t ldy,
+                            float eps, void* stream);
+// dx = rstd * (dy - mean(dy) - xhat * mean(dy * xhat)), xhat recomputed from x and the saved statistics.
+FU_API int fu_layernorm_bwd(const void* dy, const void* x, const float* stats, void* dx, int64_t rows, int64_t cols,
+                            int64_t ld, void* stream);
+
 // ---- block-scaled fp8 payloads ----------------------------------------------------------------------
 // `blocks` runs of 128 bf16 values <-> `blocks` packed rows of 144 bytes (128 e4m3 + fp32 scale + pad).
 FU_API int fu_quant_e4m3_block128(const void* x_bf16, void* packed, int64_t blocks, void* stream);
 FU_API int fu_dequant_e4m3_block128(const void* packed, void* x_bf16, int64_t blocks, void* stream);
+
+// The all-to-all of a (b, s, n, 128) bf16 tensor with the payload carried as block-scaled e4m3, in
+// one launch: quantised in the store path into the peers' windows (packed rows of 144 bytes),
+// expanded into the bf16 result `out` after the closing handshake. `routes` are the routes of the
+// bf16 plan (byte quantities of 256-byte rows); the launcher rescales the destination side.
+// `win_bytes` is the size of every window in PACKED bytes, `out_rows` the (token, head) rows of
+// the result, `src_bytes` the extent of the input.
+typedef struct FuA2AFp8Args {
+    const void* src;
+    void*       out;
+    void*       peer_win[FU_MAX_WORLD];
+    FuCtrl*     peer_ctrl[FU_MAX_WORLD];
+    int64_t     win_bytes, src_bytes, out_rows;
+    int32_t     rank, world, n_routes, flags, ctas;
+    uint32_t    timeout_ms;
+    FuRoute     routes[FU_MAX_WORLD];
+} FuA2AFp8Args;
+FU_API int fu_a2a4d_fp8(const FuA2AFp8Args* args, void* stream);
+FU_API int fu_a2a4d_fp8_check(const FuA2AFp8Args* args);  // the argument checks alone; no CUDA call
 
 FU_API const char* fu_last_error(void);
 FU_API const char* fu_build_info(void);  // "sm_100a;<nvcc version>;<library version>"

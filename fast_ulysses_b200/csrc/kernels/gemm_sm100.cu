@@ -28,6 +28,8 @@ struct PlainEpi {
     const float*         bias;
     int64_t              ldc;
     int                  M, N, act;
+    const __nv_bfloat16* aux;    // act 3: where the tanh-form GELU's derivative is evaluated
+    __nv_bfloat16*       c_pre;  // optional second output: the value before the activation
 
     __device__ void open(int) {}
     __device__ void close(int) {}
@@ -40,6 +42,12 @@ struct PlainEpi {
     __device__ __forceinline__ static float gelu_erf(float x)
     {
         return 0.5f * x * (1.0f + erff(x * 0.7071067811865476f));
+    }
+    __device__ __forceinline__ static float gelu_tanh_grad(float x)
+    {
+        const float x2 = x * x;
+        const float th = tanhf(0.7978845608028654f * (x + 0.044715f * x * x2));
+        return 0.5f * (1.0f + th) + 0.5f * x * (1.0f - th * th) * 0.7978845608028654f * (1.0f + 0.134145f * x2);
     }
 
     __device__ void tile(uint32_t tmem_acc, int mt, int nt, int quarter, int lane)
@@ -68,6 +76,32 @@ struct PlainEpi {
                 for (int j = 0; j < 32; ++j) {
                     if (col0 + j < N) {
                         v[j] += bias[col0 + j];
+                    }
+                }
+            }
+            if (c_pre) {  // the pre-activation, for the backward (whole 8-column groups only: N % 8 == 0 is checked)
+                uint4* pre = reinterpret_cast<uint4*>(c_pre + static_cast<int64_t>(row) * ldc + col0);
+#pragma unroll
+                for (int g8 = 0; g8 < 4; ++g8) {
+                    if (col0 + g8 * 8 + 8 <= N) {
+                        pre[g8] = make_uint4(pack_bf16(v[g8 * 8 + 0], v[g8 * 8 + 1]), pack_bf16(v[g8 * 8 + 2], v[g8 * 8 + 3]),
+                                             pack_bf16(v[g8 * 8 + 4], v[g8 * 8 + 5]), pack_bf16(v[g8 * 8 + 6], v[g8 * 8 + 7]));
+                    }
+                }
+            }
+            if (act == 3) {
+                const __nv_bfloat16* at = aux + static_cast<int64_t>(row) * ldc + col0;
+#pragma unroll
+                for (int g8 = 0; g8 < 4; ++g8) {
+                    if (col0 + g8 * 8 + 8 <= N) {
+                        const uint4           av = *reinterpret_cast<const uint4*>(at + g8 * 8);
+                        const __nv_bfloat162* ap = reinterpret_cast<const __nv_bfloat162*>(&av);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const float2 f = __bfloat1622float2(ap[j]);
+                            v[g8 * 8 + 2 * j] *= gelu_tanh_grad(f.x);
+                            v[g8 * 8 + 2 * j + 1] *= gelu_tanh_grad(f.y);
+                        }
                     }
                 }
             }
@@ -514,6 +548,15 @@ extern "C" int fu_gemm_bf16(const FuGemmArgs* g, void* stream)
     a.epi.M        = a.core.M;
     a.epi.N        = a.core.N;
     a.epi.act      = g->act;
+    a.epi.aux      = static_cast<const __nv_bfloat16*>(g->aux);
+    a.epi.c_pre    = static_cast<__nv_bfloat16*>(g->c_pre);
+    if (g->act < 0 || g->act > 3 || (g->act == 3 && !g->aux)) {
+        return fu::fail(FU_E_ARG, "fu_gemm_bf16: act=%d (0..3; 3 needs aux)", g->act);
+    }
+    if ((g->aux || g->c_pre) && ((g->n % 8) || (reinterpret_cast<uintptr_t>(g->aux) & 15u)
+                                 || (reinterpret_cast<uintptr_t>(g->c_pre) & 15u))) {
+        return fu::fail(FU_E_ARG, "fu_gemm_bf16: aux / c_pre need n %% 8 == 0 and 16-byte aligned rows");
+    }
     rc             = set_smem(gemm_plain_kernel);
     if (rc != FU_OK) {
         return rc;
@@ -587,7 +630,7 @@ extern "C" int fu_qkv_rope_scatter(const FuQkvArgs* q, void* stream)
     const int n_normed = q->n_types > 0 ? q->n_normed : 2;
     QkvArgs a{};
     rc = fill_core(a.core, q->x, q->w, q->m, static_cast<int64_t>(n_types) * q->heads * HEAD_DIM, q->k, q->ldx, q->ldw,
-                           q->err);
+                   q->err, (q->flags & FU_QKV_W_KN) ? FU_GEMM_B_KN : 0);
     if (rc != FU_OK) {
         return rc;
     }

@@ -26,21 +26,27 @@ __device__ inline void hs_report(FuCtrl* own, uint32_t code, uint32_t peer, uint
     }
 }
 
-// One full warp: lane p < world announces `value` to rank p.
-__device__ inline void hs_announce(const Peers& p, uint64_t value)
+// One full warp: lane p < world announces `value` to rank p. With `slot >= 0` the announcement
+// carries a byte for rank p's FuCtrl::slot_of (where this rank wants the payload of this call):
+// written first by the same thread to the same rank, so the release below orders it.
+__device__ inline void hs_announce(const Peers& p, uint64_t value, int slot = -1)
 {
     const int lane = threadIdx.x & 31;
     if (lane < p.world && !p.mute) {
+        if (slot >= 0) {
+            *reinterpret_cast<volatile uint8_t*>(&p.ctrl[lane]->slot_of[p.rank]) = static_cast<uint8_t>(slot);
+        }
         ptx::red_release_sys_max(&p.ctrl[lane]->flags[p.rank], value);
     }
 }
 
-// One full warp: lane p < world waits for rank p. False on every lane after the time limit.
-__device__ inline bool hs_await(const Peers& p, uint64_t target, uint32_t code)
+// One full warp: lane p < world waits until rank p has announced at least `target`, for the ranks
+// named in `who` (bit p). False on every lane after the time limit, with the missing rank recorded.
+__device__ inline bool hs_await(const Peers& p, uint64_t target, uint32_t code, uint32_t who = 0xffffffffu)
 {
     const int lane = threadIdx.x & 31;
     bool      ok   = true;
-    if (lane < p.world) {
+    if (lane < p.world && ((who >> lane) & 1u)) {
         const uint64_t t0    = ptx::globaltimer_ns();
         uint32_t       spins = 0;
         uint64_t       seen;

@@ -264,17 +264,6 @@ __device__ __forceinline__ void mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uin
         "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
-// fp8 (e4m3/e5m2) inputs, fp32 accumulate.
-__device__ __forceinline__ void mma_f8_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                          uint32_t accumulate)
-{
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
-        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
 // The mbarrier receives one arrival once every MMA issued so far by this thread has completed.
 __device__ __forceinline__ void mma_commit(uint64_t* bar)
 {
@@ -444,8 +433,8 @@ __device__ __forceinline__ uint64_t desc_advance(uint64_t desc, uint32_t bytes)
     return desc + static_cast<uint64_t>(bytes >> 4);
 }
 
-// Instruction descriptor for kind::f16 / kind::f8f6f4 with fp32 accumulation.
-//   fmt: kind::f16 0 = fp16, 1 = bf16; kind::f8f6f4 0 = e4m3, 1 = e5m2.
+// Instruction descriptor for kind::f16 with fp32 accumulation.
+//   fmt: 0 = fp16, 1 = bf16.
 //   *_mn_major: 1 when that operand's contiguous axis is M (or N) rather than K.
 __host__ __device__ constexpr uint32_t make_idesc(uint32_t a_fmt, uint32_t b_fmt, uint32_t m, uint32_t n,
                                                   uint32_t a_mn_major, uint32_t b_mn_major)

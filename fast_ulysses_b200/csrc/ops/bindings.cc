@@ -5,6 +5,7 @@
 // one kernel launch per collective (handshakes, payload and copy-out fused), the input is read in
 // place by that kernel (no staging copy, strided views accepted), and CPU tensors run the same
 // plan over the process group's all-to-all.
+#include <nvtx3/nvToolsExt.h>
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDACachingAllocator.h>
 #include <c10/cuda/CUDAGuard.h>
@@ -185,6 +186,16 @@ Prepared prepare(Group& g, const at::Tensor& input, int64_t mode, const Splits& 
     return p;
 }
 
+// An NVTX range around the host side of one collective (argument checks, plan lookup, launch):
+// a timeline profiler shows which call of the library a kernel on the stream belongs to. The
+// header-only NVTX costs a null check when no profiler is attached.
+struct NvtxRange {
+    explicit NvtxRange(const char* name) { nvtxRangePushA(name); }
+    ~NvtxRange() { nvtxRangePop(); }
+    NvtxRange(const NvtxRange&)            = delete;
+    NvtxRange& operator=(const NvtxRange&) = delete;
+};
+
 void run_prepared(Group& g, Prepared& p, cudaStream_t stream, int extra_flags)
 {
     if (!g.on_cuda()) {
@@ -233,6 +244,7 @@ void refuse_vmap(const c10::OperatorHandle& op, c10::Stack*)
 at::Tensor all_to_all_4d(const GroupPtr& group, const at::Tensor& input, int64_t mode, const Splits& seq,
                          const Splits& heads)
 {
+    const NvtxRange range(mode == 0 ? "fast_ulysses_b200::all_to_all_4d[mode 0]" : "fast_ulysses_b200::all_to_all_4d[mode 1]");
     Prepared p = prepare(*group, input, mode, seq, heads, std::nullopt, Role::kSync, false);
     if (group->on_cuda()) {
         const c10::cuda::CUDAGuard guard(input.device());
@@ -253,6 +265,8 @@ at::Tensor all_to_all_4d_meta(const GroupPtr& group, const at::Tensor& input, in
 void all_to_all_4d_out(const GroupPtr& group, const at::Tensor& input, int64_t mode, const Splits& seq,
                        const Splits& heads, at::Tensor out)
 {
+    const NvtxRange range(mode == 0 ? "fast_ulysses_b200::all_to_all_4d_out[mode 0]"
+                                    : "fast_ulysses_b200::all_to_all_4d_out[mode 1]");
     Prepared p = prepare(*group, input, mode, seq, heads, out, Role::kSync, false);
     if (group->on_cuda()) {
         const c10::cuda::CUDAGuard guard(input.device());
@@ -283,6 +297,7 @@ at::Tensor run_async(Group& g, const at::Tensor& input, int64_t mode, const Spli
 {
     g.check_alive();
     require_backend(g, input, "input");
+    const NvtxRange range("fast_ulysses_b200::all_to_all_4d_async");
     if (!g.on_cuda()) {
         Prepared p = prepare(g, input, mode, seq, heads, out, Role::kAsync, false);
         run_prepared(g, p, nullptr, 0);

@@ -8,9 +8,11 @@ Forward (three kernels, no separate exchange, no permute, no staging copy):
   3. ``fu_pull_outproj``      the output projection pulls its A operand from the peers' attention
      outputs tile by tile (mode 1 of the all-to-all is the load address)
 Backward mirrors it: the gradient of the attention output is scattered to the head owners from
-the epilogue of the dgrad GEMM (same kernel as 1 without norm/RoPE), tcgen05 flash attention
-backward, one ``all_to_all_4d`` (mode 1) brings dq/dk/dv home, a fused RMSNorm/RoPE backward
-feeds the dgrad/wgrad GEMMs.
+the epilogue of the dgrad GEMM (same kernel as 1 without norm/RoPE, reading W_o as stored),
+tcgen05 flash attention backward writes dq/dk/dv into a symmetric buffer, and ONE kernel
+(``fu_pull_qkv_grads``) pulls them home from the head owners over NVLink while undoing RoPE and
+RMSNorm on the way and writes the operand of the dgrad/wgrad GEMMs: no stand-alone exchange, no
+separate norm/RoPE backward, no slice copy, no transposed weight.
 
 The reference ships no model code; its example (examples/dit_attention.py:21-63) wraps nn.Linear
 and torch SDPA around two all_to_all_4d calls. ``reference_attention`` below is that composition,
@@ -23,6 +25,7 @@ import math
 
 import torch
 import torch.nn as nn
+from torch.cuda import nvtx
 
 from ..ops import _ckernels as ck
 from ..ops import attention as fa
@@ -50,34 +53,44 @@ class SymmBuffer:
 
 class _SPAttention(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, w_qkv, gamma_q, gamma_k, w_o, b_o, mod):
+    def forward(ctx, x, w_qkv, gamma_q, gamma_k, w_o, b_o, residual, mod):
         b, s_local, hidden = x.shape
         m = b * s_local
         x2 = x.reshape(m, hidden)
         if x2.stride(1) != 1 or x2.stride(0) % 8:
             x2 = x2.contiguous()
         N = mod.heads
-        need_grad = any(ctx.needs_input_grad[:6])
+        need_grad = any(ctx.needs_input_grad[:7])
         # q, k, v and the attention output live in the module's symmetric buffers, not in tensors
         # saved for backward: a second forward overwrites them. Number the forwards so that a
         # backward which would read another call's activations refuses instead.
         mod._forward_count += 1
         y_save = torch.empty(m, 2 * N * HEAD_DIM, dtype=torch.bfloat16, device=x.device) if need_grad else None
-        mod._launch_scatter(x2, w_qkv, mod.qkv_win, 3, 2, gamma_q, gamma_k, y_save)
+        with nvtx.range("fast_ulysses_b200::qkv_norm_rope_scatter"):
+            mod._launch_scatter(x2, w_qkv, mod.qkv_win, 3, 2, gamma_q, gamma_k, y_save)
         q, k, v = mod.q_view, mod.k_view, mod.v_view
-        _, lse = fa.fmha_fwd(q, k, v, out=mod.o_view)
+        with nvtx.range("fast_ulysses_b200::fmha_fwd"):
+            _, lse = fa.fmha_fwd(q, k, v, out=mod.o_view)
         gather = torch.empty(m, N * HEAD_DIM, dtype=torch.bfloat16, device=x.device)
         out = torch.empty(m, hidden, dtype=torch.bfloat16, device=x.device)
         ready = mod._ready_flags(m)
-        outproj.pull_outproj_raw(w_o, out, gather, ready, s_local=s_local, seq_off=mod.seq_off, s_total=mod.s_total,
-                                 head_splits=mod.head_splits, rank=mod.rank, peer_o=mod.o_buf.base, ctrl=mod.o_buf.ctrl,
-                                 o_bytes=mod._region,
-                                 bias=mod._f32("b_o", b_o) if b_o is not None else None, timeout_ms=mod.timeout_ms)
+        res2 = None
+        if residual is not None:  # added in the out-projection's epilogue
+            res2 = residual.reshape(m, hidden)
+            if not res2.is_contiguous():
+                res2 = res2.contiguous()
+        with nvtx.range("fast_ulysses_b200::pull_outproj"):
+            outproj.pull_outproj_raw(w_o, out, gather, ready, s_local=s_local, seq_off=mod.seq_off,
+                                     s_total=mod.s_total, head_splits=mod.head_splits, rank=mod.rank,
+                                     peer_o=mod.o_buf.base, ctrl=mod.o_buf.ctrl, o_bytes=mod._region,
+                                     bias=mod._f32("b_o", b_o) if b_o is not None else None,
+                                     residual=res2, timeout_ms=mod.timeout_ms, ctas=mod._fused_ctas())
         if need_grad:
             ctx.save_for_backward(x2, w_qkv, gamma_q, gamma_k, w_o, y_save, gather, lse)
             ctx.mod = mod
             ctx.forward_id = mod._forward_count
             ctx.has_bias = b_o is not None
+            ctx.has_residual = residual is not None
             ctx.x_shape = x.shape
         return out.view(b, s_local, hidden)
 
@@ -100,24 +113,29 @@ class _SPAttention(torch.autograd.Function):
         db_o = dy2.sum(0, dtype=torch.float32).to(dy.dtype) if ctx.has_bias else None
         # dW_o[n, k] = sum_m dy[m, n] A[m, k]
         dw_o = gemm.gemm_bf16(dy2, gather, a_km=True, b_kn=True)
-        # dA = dy W_o, scattered to the head owners from the GEMM epilogue (mode-0 direction)
-        mod._launch_scatter(dy2, w_o.t().contiguous(), mod.do_win, 1, 0, None, None, None)
-        dqkv = torch.empty(3, b, mod.s_total, mod.n_local, HEAD_DIM, dtype=torch.bfloat16, device=dy.device)
-        fa.fmha_bwd(mod.q_view, mod.k_view, mod.v_view, mod.o_view, lse, mod.do_view,
-                    out=(dqkv[0], dqkv[1], dqkv[2]))
-        # dq, dk, dv go home in one exchange (mode 1), the three tensors folded into the batch axis
-        back = mod.group.all_to_all_4d(dqkv.view(3 * b, mod.s_total, mod.n_local, HEAD_DIM), mode=1,
-                                       seq_splits=mod.seq_splits, head_splits=mod.head_splits)
-        back = back.view(3, m, N * HEAD_DIM)
+        # dA = dy W_o, scattered to the head owners from the GEMM epilogue (mode-0 direction); W_o is
+        # (hidden, heads * 128) = (contraction, output) as stored, so nothing is transposed
+        with nvtx.range("fast_ulysses_b200::dout_scatter"):
+            mod._launch_scatter(dy2, w_o, mod.do_win, 1, 0, None, None, None, w_kn=True)
+        with nvtx.range("fast_ulysses_b200::fmha_bwd"):
+            fa.fmha_bwd(mod.q_view, mod.k_view, mod.v_view, mod.o_view, lse, mod.do_view,
+                        out=(mod.dq_view, mod.dk_view, mod.dv_view))
+        # dq, dk, dv come home inside the kernel that undoes RoPE and RMSNorm (mode-1 direction)
         dyqkv = torch.empty(m, 3 * N * HEAD_DIM, dtype=torch.bfloat16, device=dy.device)
         dgq = torch.zeros(HEAD_DIM, dtype=torch.float32, device=dy.device)
         dgk = torch.zeros(HEAD_DIM, dtype=torch.float32, device=dy.device)
-        qkv.qk_norm_rope_bwd(back[0], back[1], y_save, dyqkv, mod.rope, gamma_q, gamma_k, dgq, dgk, heads=N,
-                             s_local=s_local, eps=mod.eps)
-        dyqkv[:, 2 * N * HEAD_DIM:].copy_(back[2])
+        R = mod._region
+        with nvtx.range("fast_ulysses_b200::pull_qkv_grads"):
+            qkv.pull_qkv_grads_raw(dyqkv, y_save, mod.rope, mod._f32("gamma_q", gamma_q), mod._f32("gamma_k", gamma_k),
+                                   dgq, dgk, heads=N, s_local=s_local, seq_off=mod.seq_off, s_total=mod.s_total,
+                                   head_splits=mod.head_splits, rank=mod.rank, peer_dq=mod.dqkv_buf.base,
+                                   peer_dk=[p + R for p in mod.dqkv_buf.base],
+                                   peer_dv=[p + 2 * R for p in mod.dqkv_buf.base], ctrl=mod.dqkv_buf.ctrl,
+                                   src_bytes=R, eps=mod.eps, timeout_ms=mod.timeout_ms)
         dx = gemm.gemm_bf16(dyqkv, w_qkv, b_kn=True).view(b, s_local, hidden)
         dw_qkv = gemm.gemm_bf16(dyqkv, x2, a_km=True, b_kn=True)
-        return dx, dw_qkv, dgq.to(gamma_q.dtype), dgk.to(gamma_k.dtype), dw_o, db_o, None
+        return (dx, dw_qkv, dgq.to(gamma_q.dtype), dgk.to(gamma_k.dtype), dw_o, db_o,
+                dy if ctx.has_residual else None, None)
 
 
 class UlyssesSelfAttention(nn.Module):
@@ -164,12 +182,16 @@ class UlyssesSelfAttention(nn.Module):
         self.qkv_win = SymmBuffer(group, 3 * region)
         self.o_buf = SymmBuffer(group, region)
         self.do_win = SymmBuffer(group, region)
+        self.dqkv_buf = SymmBuffer(group, 3 * region)  # dq | dk | dv of this rank's heads, pulled by the token owners
         shape = (batch, total, self.n_local, HEAD_DIM)
         self.q_view = self.qkv_win.view(0, shape)
         self.k_view = self.qkv_win.view(region, shape)
         self.v_view = self.qkv_win.view(2 * region, shape)
         self.o_view = self.o_buf.view(0, shape)
         self.do_view = self.do_win.view(0, shape)
+        self.dq_view = self.dqkv_buf.view(0, shape)
+        self.dk_view = self.dqkv_buf.view(region, shape)
+        self.dv_view = self.dqkv_buf.view(2 * region, shape)
         self._ready = None
         self._forward_count = 0
         self._f32_cache: dict[str, tuple[int, torch.Tensor]] = {}
@@ -183,18 +205,37 @@ class UlyssesSelfAttention(nn.Module):
             self._f32_cache[name] = hit
         return hit[1]
 
+    def _fused_ctas(self) -> int:
+        """How many CTAs a fused GEMM kernel of this block may take right now (0 = the whole device).
+
+        The fused kernels are persistent, one CTA per SM, and their CTAs wait on peers; an
+        asynchronous exchange of the same group is a kernel of the same kind on another stream.
+        If one held every SM on this rank while the other could not start here, and the opposite
+        happened on a peer, each would wait for a kernel that cannot run. So while the group's comm
+        stream has work queued, a fused kernel leaves the SMs an asynchronous exchange takes (a
+        third of the device) free; with the comm stream idle it takes everything. All ranks issue
+        the same calls in the same order, so a rank that sees its comm stream idle has an exchange
+        that every peer has already been able to start."""
+        comm = getattr(self.group, "_comm_stream", None)
+        if self.world == 1 or comm is None or comm.query():
+            return 0
+        sms = torch.cuda.get_device_properties(self.group.device).multi_processor_count
+        return sms - sms // 3
+
     def _ready_flags(self, m: int) -> torch.Tensor:
         n = ((m + 127) // 128) * self.world
         if self._ready is None or self._ready.numel() < n:
             self._ready = torch.zeros(n, dtype=torch.int32, device=self.group.device)
         return self._ready
 
-    def _launch_scatter(self, x2, w, win: SymmBuffer, n_types, n_normed, gamma_q, gamma_k, y_save):
+    def _launch_scatter(self, x2, w, win: SymmBuffer, n_types, n_normed, gamma_q, gamma_k, y_save, w_kn=False):
+        """``w_kn``: the weight is (contraction, output) as stored instead of (output, contraction)."""
         import ctypes as C
 
         a = ck.FuQkvArgs()
         a.x, a.w = x2.data_ptr(), w.data_ptr()
         a.m, a.k, a.ldx, a.ldw = x2.shape[0], x2.shape[1], x2.stride(0), w.stride(0)
+        a.flags = ck.FU_QKV_W_KN if w_kn else 0
         a.heads = self.heads
         a.s_local, a.seq_off, a.s_total = self.s_local, self.seq_off, self.s_total
         a.eps = self.eps
@@ -209,17 +250,21 @@ class UlyssesSelfAttention(nn.Module):
             a.win_v[p] = win.base[p] + 2 * self._region
             a.peer_ctrl[p] = win.ctrl[p]
         a.timeout_ms = self.timeout_ms
+        a.ctas = self._fused_ctas()
         a.err = gemm.error_word(x2.device).data_ptr()
         a.n_types, a.n_normed = n_types, n_normed
         a.win_bytes = self._region
         if y_save is not None:
             a.y_save, a.ld_y = y_save.data_ptr(), y_save.stride(0)
-        assert w.shape[0] == n_types * self.heads * HEAD_DIM and x2.dtype == torch.bfloat16
+        assert w.shape[1 if w_kn else 0] == n_types * self.heads * HEAD_DIM and x2.dtype == torch.bfloat16
+        assert w.shape[0 if w_kn else 1] == x2.shape[1] and w.stride(1) == 1
         ck.check(ck.lib().fu_qkv_rope_scatter(C.byref(a), ck.stream_ptr()))
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, residual: torch.Tensor | None = None) -> torch.Tensor:
+        """``residual`` (same shape as the result) is added in the output projection's epilogue."""
         assert x.shape[0] == self.batch and x.shape[1] == self.s_local and x.dtype == torch.bfloat16, x.shape
-        return _SPAttention.apply(x, self.w_qkv, self.gamma_q, self.gamma_k, self.w_o, self.b_o, self)
+        assert residual is None or (residual.shape == x.shape and residual.dtype == torch.bfloat16)
+        return _SPAttention.apply(x, self.w_qkv, self.gamma_q, self.gamma_k, self.w_o, self.b_o, residual, self)
 
 
 def reference_attention(x_full, w_qkv, gamma_q, gamma_k, w_o, b_o, heads, grid, eps=1e-6, compute=torch.float32):

@@ -30,8 +30,8 @@ def bench_attention_block(group, world: int, rank: int, time_steps, flush, steps
 
     out = {"config": {"hidden": HIDDEN, "heads": HEADS, "tokens": GRID[0] * GRID[1] * GRID[2],
                       "per_rank_x": [1, s_local, HIDDEN], "kernels": "fused qkv+norm+rope+scatter, tcgen05 fmha, "
-                      "pull+outproj; backward: scatter-epilogue dgrad, tcgen05 fmha bwd, a2a mode 1, "
-                      "norm/rope bwd, tcgen05 dgrad/wgrad"}}
+                      "pull+outproj; backward: scatter-epilogue dgrad, tcgen05 fmha bwd, fused pull of dq/dk/dv + "
+                      "norm/rope backward, tcgen05 dgrad/wgrad"}}
     out["fwd_ms"] = time_steps(fwd, steps, warmup, world, flush)
     out["fwd_bwd_ms"] = time_steps(step, steps, warmup, world, flush)
     gemm.check_errors()

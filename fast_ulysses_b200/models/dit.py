@@ -1,9 +1,11 @@
 """A Wan2.1-14B-shaped DiT block stack (self-attention only) on the fused sequence-parallel kernels.
 
 Block: x + Attn(LN(x)); x + FFN(LN(x)) with FFN = Linear(5120 -> 13824) -> GELU(tanh) ->
-Linear(13824 -> 5120). Every contraction runs on the tcgen05 GEMM; LayerNorm and GELU are plain
-PyTorch elementwise ops. ``reference_forward`` is the same stack without sequence parallelism on
-one device, the oracle for the multi-GPU tests.
+Linear(13824 -> 5120). Every contraction runs on the tcgen05 GEMM and everything between the
+contractions lives in an epilogue: GELU (and, backward, its derivative), both residual adds and
+the biases; LayerNorm is one kernel forward and one backward. No eager PyTorch elementwise kernel
+runs inside a block. ``reference_forward`` is the same stack without sequence parallelism on one
+device, the oracle for the multi-GPU tests.
 """
 
 from __future__ import annotations
@@ -12,7 +14,8 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-from ..ops.gemm import linear
+from ..ops.gemm import feed_forward
+from ..ops.norm import layer_norm
 from .attention import UlyssesSelfAttention, reference_attention
 
 
@@ -28,9 +31,8 @@ class DiTBlock(nn.Module):
         self.b2 = nn.Parameter(torch.zeros(hidden, device=dev).bfloat16())
 
     def forward(self, x):
-        x = x + self.attn(F.layer_norm(x, (self.hidden,), eps=1e-6))
-        h = F.gelu(linear(F.layer_norm(x, (self.hidden,), eps=1e-6), self.w1, self.b1), approximate="tanh")
-        return x + linear(h, self.w2, self.b2)
+        x = self.attn(layer_norm(x), residual=x)  # x + Attn(LN(x)): the add is the out-projection's epilogue
+        return feed_forward(layer_norm(x), self.w1, self.b1, self.w2, self.b2, residual=x)
 
 
 class DiTStack(nn.Module):

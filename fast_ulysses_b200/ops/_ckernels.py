@@ -20,6 +20,7 @@ FU_A2A_EARLY_PUBLISH = 4
 FU_A2A_LDST = 8
 FU_A2A_MUTE = 16
 FU_A2A_MINOR_SHARE = 32
+FU_QKV_W_KN = 64
 
 
 class FuRoute(C.Structure):
@@ -60,7 +61,18 @@ def lib() -> C.CDLL:
                      "fu_qk_norm_rope_bwd"):
             getattr(_lib, name).restype = C.c_int
             getattr(_lib, name).argtypes = [C.c_void_p, C.c_void_p]
-        for name in ("fu_a2a4d_check", "fu_qkv_rope_scatter_check", "fu_pull_outproj_check"):
+        _lib.fu_layernorm_fwd.restype = C.c_int
+        _lib.fu_layernorm_fwd.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int64,
+                                          C.c_float, C.c_void_p]
+        _lib.fu_layernorm_bwd.restype = C.c_int
+        _lib.fu_layernorm_bwd.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64,
+                                          C.c_void_p]
+        _lib.fu_pull_qkv_grads.restype = C.c_int
+        _lib.fu_pull_qkv_grads.argtypes = [C.c_void_p, C.c_void_p]
+        _lib.fu_a2a4d_fp8.restype = C.c_int
+        _lib.fu_a2a4d_fp8.argtypes = [C.c_void_p, C.c_void_p]
+        for name in ("fu_a2a4d_check", "fu_qkv_rope_scatter_check", "fu_pull_outproj_check", "fu_pull_qkv_grads_check",
+                     "fu_a2a4d_fp8_check"):
             getattr(_lib, name).restype = C.c_int
             getattr(_lib, name).argtypes = [C.c_void_p]
     return _lib
@@ -81,7 +93,7 @@ class FuGemmArgs(C.Structure):
     _fields_ = [("a", C.c_void_p), ("b", C.c_void_p), ("c", C.c_void_p), ("m", C.c_int64), ("n", C.c_int64),
                 ("k", C.c_int64), ("lda", C.c_int64), ("ldb", C.c_int64), ("ldc", C.c_int64), ("bias", C.c_void_p),
                 ("residual", C.c_void_p), ("act", C.c_int32), ("ctas", C.c_int32), ("err", C.c_void_p),
-                ("flags", C.c_int32)]
+                ("flags", C.c_int32), ("aux", C.c_void_p), ("c_pre", C.c_void_p)]
 
 
 class FuQkvArgs(C.Structure):
@@ -130,3 +142,21 @@ class FuNormRopeBwdArgs(C.Structure):
                 ("gamma_q", C.c_void_p), ("gamma_k", C.c_void_p), ("dgamma_q", C.c_void_p), ("dgamma_k", C.c_void_p),
                 ("m", C.c_int64), ("s_local", C.c_int64), ("ld_y", C.c_int64), ("ld_dy", C.c_int64),
                 ("heads", C.c_int32), ("eps", C.c_float)]
+
+
+class FuPullGradsArgs(C.Structure):
+    _fields_ = [("peer_dq", C.c_void_p * FU_MAX_WORLD), ("peer_dk", C.c_void_p * FU_MAX_WORLD),
+                ("peer_dv", C.c_void_p * FU_MAX_WORLD), ("peer_ctrl", C.c_void_p * FU_MAX_WORLD),
+                ("src_bytes", C.c_int64), ("y", C.c_void_p), ("dy", C.c_void_p), ("rope", C.c_void_p),
+                ("gamma_q", C.c_void_p), ("gamma_k", C.c_void_p), ("dgamma_q", C.c_void_p), ("dgamma_k", C.c_void_p),
+                ("m", C.c_int64), ("s_local", C.c_int64), ("seq_off", C.c_int64), ("s_total", C.c_int64),
+                ("ld_y", C.c_int64), ("ld_dy", C.c_int64), ("heads", C.c_int32), ("rank", C.c_int32),
+                ("world", C.c_int32), ("head_splits", C.c_int32 * FU_MAX_WORLD), ("flags", C.c_int32),
+                ("timeout_ms", C.c_uint32), ("eps", C.c_float)]
+
+
+class FuA2AFp8Args(C.Structure):
+    _fields_ = [("src", C.c_void_p), ("out", C.c_void_p), ("peer_win", C.c_void_p * FU_MAX_WORLD),
+                ("peer_ctrl", C.c_void_p * FU_MAX_WORLD), ("win_bytes", C.c_int64), ("src_bytes", C.c_int64),
+                ("out_rows", C.c_int64), ("rank", C.c_int32), ("world", C.c_int32), ("n_routes", C.c_int32),
+                ("flags", C.c_int32), ("ctas", C.c_int32), ("timeout_ms", C.c_uint32), ("routes", FuRoute * FU_MAX_WORLD)]

@@ -85,3 +85,34 @@ def qk_norm_rope_bwd(dq, dk, y_save, dy, rope, gamma_q, gamma_k, dgamma_q, dgamm
     a.m, a.s_local, a.ld_y, a.ld_dy = m, s_local, y_save.stride(0), dy.stride(0)
     a.heads, a.eps = heads, eps
     ck.check(ck.lib().fu_qk_norm_rope_bwd(C.byref(a), ck.stream_ptr()))
+
+
+def pull_qkv_grads_raw(dy: torch.Tensor, y_save: torch.Tensor, rope: torch.Tensor, gamma_q: torch.Tensor,
+                       gamma_k: torch.Tensor, dgamma_q: torch.Tensor, dgamma_k: torch.Tensor, *, heads: int,
+                       s_local: int, seq_off: int, s_total: int, head_splits: list[int], rank: int,
+                       peer_dq: list[int], peer_dk: list[int], peer_dv: list[int], ctrl: list[int], src_bytes: int,
+                       eps: float = 1e-6, flags: int = 0, timeout_ms: int = 10000) -> None:
+    """The exchange that brings dq, dk, dv home fused with the backward of RMSNorm -> RoPE
+    (csrc/kernels/elementwise.cu:fu_pull_qkv_grads). ``peer_d*`` are the addresses of every rank's
+    (b, s_total, head_splits[p], 128) bf16 gradient buffers, ``src_bytes`` the bytes behind each;
+    ``dy`` (m, 3*heads*128) receives d(projection) for q | k | v; ``dgamma_*`` fp32[128] accumulate."""
+    m = dy.shape[0]
+    assert dy.dtype == torch.bfloat16 and dy.shape[1] == 3 * heads * HEAD_DIM and dy.stride(1) == 1
+    assert y_save.dtype == torch.bfloat16 and y_save.shape == (m, 2 * heads * HEAD_DIM) and y_save.stride(1) == 1
+    assert rope.dtype == torch.float32 and rope.shape == (s_local, HEAD_DIM // 2, 2) and rope.is_contiguous()
+    for t in (gamma_q, gamma_k, dgamma_q, dgamma_k):
+        assert t.dtype == torch.float32 and t.numel() == HEAD_DIM and t.is_contiguous()
+    a = ck.FuPullGradsArgs()
+    world = len(head_splits)
+    for p in range(world):
+        a.peer_dq[p], a.peer_dk[p], a.peer_dv[p], a.peer_ctrl[p] = peer_dq[p], peer_dk[p], peer_dv[p], ctrl[p]
+        a.head_splits[p] = head_splits[p]
+    a.src_bytes = src_bytes
+    a.y, a.dy, a.rope = y_save.data_ptr(), dy.data_ptr(), rope.data_ptr()
+    a.gamma_q, a.gamma_k = gamma_q.data_ptr(), gamma_k.data_ptr()
+    a.dgamma_q, a.dgamma_k = dgamma_q.data_ptr(), dgamma_k.data_ptr()
+    a.m, a.s_local, a.seq_off, a.s_total = m, s_local, seq_off, s_total
+    a.ld_y, a.ld_dy = y_save.stride(0), dy.stride(0)
+    a.heads, a.rank, a.world = heads, rank, world
+    a.flags, a.timeout_ms, a.eps = flags, timeout_ms, eps
+    ck.check(ck.lib().fu_pull_qkv_grads(C.byref(a), ck.stream_ptr()))

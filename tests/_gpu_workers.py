@@ -249,16 +249,41 @@ def validation_uniform(rank, world):
     rejects("does not support autograd", lambda: g.all_to_all_4d_async(ok.clone().requires_grad_()))
     rejects("not both", lambda: g.all_to_all_4d_async(ok, out=zc, lend=True), ValueError)
     rejects("does not support torch.vmap", lambda: torch.vmap(lambda t: g.all_to_all_4d(t))(ok.unsqueeze(0)))
+    # every op of the library refuses a batched input, not only the functional one
+    ops = torch.ops.fast_ulysses_b200
+    batched = ok.unsqueeze(0)
+    rejects("does not support torch.vmap",
+            lambda: torch.vmap(lambda t: ops.all_to_all_4d_out(g._handle, t, 0, None, None, zc))(batched))
+    rejects("does not support torch.vmap",
+            lambda: torch.vmap(lambda t: ops.all_to_all_4d_staged(g._handle, t, 0, None, None, 0, rank, False))(batched))
+    rejects("does not support torch.vmap",
+            lambda: torch.vmap(lambda t: ops.all_to_all_4d_staged_out(g._handle, t, 0, None, None, zc, 0, rank))(batched))
+    rejects("does not support torch.vmap", lambda: torch.vmap(lambda t: ops.empty_output(g._handle, t, 0, None, None))(batched))
+    rejects("does not support torch.vmap",
+            lambda: torch.vmap(lambda t: ops.all_to_all_4d_timed(g._handle, t, 0, None, None))(batched))
+    # batched gradients are vmap over the backward: the same refusal, reached through autograd
+    xg = ok.clone().requires_grad_()
+    yg = g.all_to_all_4d(xg)
+    rejects("does not support torch.vmap",
+            lambda: torch.autograd.grad(yg, xg, torch.ones(3, *yg.shape, device=dev, dtype=yg.dtype),
+                                        is_grads_batched=True))
+    # empty split lists are not "no splits", also once the plan cache is warm for this shape
+    g.all_to_all_4d(ok)
+    rejects("seq_splits", lambda: g.all_to_all_4d(ok, seq_splits=[], head_splits=[]))
     held = [g.all_to_all_4d_async(ok, lend=True).wait() for _ in range(4)]
     rejects("lent results may be alive at once", lambda: g.all_to_all_4d_async(ok, lend=True))
     del held
     if torch.cuda.device_count() > world:
         other = torch.device("cuda", world)
         rejects("one group serves exactly one device", lambda: g.all_to_all_4d(ok.to(other)))
+        rejects("out", lambda: g.all_to_all_4d(ok, out=torch.empty(1, 8 * world, 2, 64, device=other,
+                                                                     dtype=torch.bfloat16)))
     g.check()
     g.destroy()
     rejects("has been destroyed", lambda: g.all_to_all_4d(ok))
     rejects("has been destroyed", lambda: g.all_to_all_4d_async(ok))
+    rejects("has been destroyed", lambda: g.all_to_all_4d(ok, out=zc))  # the zero-copy path checks too
+    rejects("has been destroyed", lambda: g.empty_output(ok))
 
 
 def _alias_of(zc, world):
@@ -310,6 +335,16 @@ def graph_replay(rank, world):
     graph = torch.cuda.CUDAGraph()
     with torch.cuda.graph(graph):
         g.all_to_all_4d(x, out=out)
+    # control: a replay must move the data by itself. If the capture had recorded nothing, every
+    # check below would be comparing `out` with what the eager call above left in it.
+    x.fill_(-3.0)
+    out.fill_(123.0)
+    torch.cuda.synchronize()
+    dist.barrier()
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.all(out == -3.0), "the captured graph did not run the collective"
+    e0 += 2
     ballast = torch.randn(4096, 4096, device=dev)
     for i in range(8):
         x.copy_(torch.full_like(x, float(i + 1)))
@@ -325,66 +360,200 @@ def graph_replay(rank, world):
 
 
 def sync_async_coexist(rank, world):
-    """Sync and async calls on unordered streams use separate windows."""
+    """Sync and async calls on unordered streams use separate windows. 2000 rounds with a rotating
+    slow rank, exact phase counts at the end, and a liveness sample: events on both streams must
+    show, in some sampled round, a synchronous call running inside the device life of the
+    asynchronous one. If they never overlap the test has not exercised what it is about (BLIND)."""
     dev = torch.device("cuda", rank)
     g = UlyssesGroup(device=dev)
-    rounds = 200
+    rounds = 2000
     xs = torch.empty(1, 256, 2 * world, 128, device=dev, dtype=torch.bfloat16)
-    bad = 0
+    big = torch.empty(1, 4096, 2 * world, 128, device=dev, dtype=torch.bfloat16)  # the async payload lasts longer
+    cur, comm = torch.cuda.current_stream(dev), g._comm_stream
+    bad, overlapped, sampled = 0, 0, 0
     for i in range(rounds):
-        a = torch.full_like(xs, float(i % 50))
-        b = torch.full_like(xs, float(100 + i % 50))
-        if rank == i % world:
+        a_val, b_val = float(i % 50), float(100 + i % 50)
+        b = torch.full_like(xs, b_val)
+        sample = i % 100 == 0
+        if sample:
+            big.fill_(a_val)
+            a = big
+        else:
+            a = torch.full_like(xs, a_val)
+        if rank == i % world and i % 10 == 0:
             torch.cuda._sleep(200000)
+        if sample:
+            a0 = torch.cuda.Event(enable_timing=True)
+            a1 = torch.cuda.Event(enable_timing=True)
+            s0 = torch.cuda.Event(enable_timing=True)
+            s1 = torch.cuda.Event(enable_timing=True)
+            a0.record(cur)  # the async call's staging copy and launch are ordered after this point
         h = g.all_to_all_4d_async(a)
+        if sample:
+            a1.record(comm)
+            s0.record(cur)
         y1 = g.all_to_all_4d(b)
         y2 = g.all_to_all_4d(b)
+        if sample:
+            s1.record(cur)
         ya = h.wait()
-        bad += int(not (torch.all(ya == float(i % 50)) and torch.all(y1 == float(100 + i % 50))
-                        and torch.all(y2 == float(100 + i % 50))))
+        bad += int(not (torch.all(ya == a_val) and torch.all(y1 == b_val) and torch.all(y2 == b_val)))
+        if sample:
+            torch.cuda.synchronize()
+            sampled += 1
+            # the sync pair started before the async call ended, and ended after the async call began
+            overlapped += int(s0.elapsed_time(a1) > 0 and a0.elapsed_time(s1) > 0)
     torch.cuda.synchronize()
     assert g._handle.epoch_debug(xs, 0) == 4 * rounds and g._handle.epoch_debug(xs, 1) == 2 * rounds
     g.check()
     g.destroy()
     assert bad == 0
+    t = torch.tensor([overlapped], device=dev)
+    dist.all_reduce(t)
+    if int(t.item()) == 0:
+        print("BLIND: no sampled round showed the synchronous calls inside the asynchronous call's life")
+    elif rank == 0:
+        print(f"liveness: {int(t.item())} of {sampled * world} sampled (round, rank) pairs overlapped")
 
 
 def window_reuse_race(rank, world):
-    """A peer's next call must not overwrite a window this rank is still reading: the opening
-    handshake makes writers wait for readers. One rotating slow reader per round."""
+    """A peer's next call must not overwrite a buffer this rank is still reading: the opening
+    handshake makes writers wait for readers, where "readers" means everything queued on the
+    calling stream. CLEAN: a slow reader on the calling stream is never torn. ARMED: the same slow
+    read on a side stream that nothing orders before the next call is outside that guarantee and
+    must see the next call's data at least once; if it never does, CLEAN proved nothing (BLIND)."""
     dev = torch.device("cuda", rank)
     g = UlyssesGroup(device=dev)
     x = torch.empty(1, 4096, 2 * world, 128, device=dev, dtype=torch.bfloat16)
     out = g.empty_output(x)
-    bad = 0
-    for i in range(40):
-        x.fill_(float(i + 1))
-        g.all_to_all_4d(x, out=out)
-        if rank == i % world:
-            torch.cuda._sleep(2_000_000)  # a slow reader: its read of `out` is queued behind this
-        snapshot = out.clone()  # ordered on the caller's stream, before this rank's next call
-        bad += int(not bool(torch.all(snapshot == float(i + 1))))
+    cur, side = torch.cuda.current_stream(dev), torch.cuda.Stream(device=dev)
+
+    def rounds(armed, n=40):
+        torn, snaps = 0, []
+        for i in range(n):
+            x.fill_(float(i + 1))
+            g.all_to_all_4d(x, out=out)
+            if armed:
+                side.wait_stream(cur)  # the read starts after this call ...
+                with torch.cuda.stream(side):
+                    torch.cuda._sleep(2_000_000)  # ... late, and nothing makes the next call wait for it
+                    snaps.append((out.clone(), float(i + 1)))
+            else:
+                if rank == i % world:
+                    torch.cuda._sleep(2_000_000)  # a slow reader: its read of `out` is queued behind this
+                snapshot = out.clone()  # ordered on the caller's stream, before this rank's next call
+                torn += int(not bool(torch.all(snapshot == float(i + 1))))
+        cur.wait_stream(side)
+        torch.cuda.synchronize()
+        torn += sum(int(not bool(torch.all(t == v))) for t, v in snaps)
+        t = torch.tensor([torn], device=dev)
+        dist.all_reduce(t)
+        return int(t.item())
+
+    clean = rounds(False)
+    armed = rounds(True)
     g.check()
     g.destroy()
-    assert bad == 0
+    assert clean == 0, f"CLEAN phase tore {clean} times"
+    if armed == 0:
+        print("BLIND: the unordered side-stream read was never overwritten; the clean result proves less than it should")
+
+
+def async_input_may_be_overwritten(rank, world):
+    """The asynchronous call's default contract: `x` may be overwritten the moment the call returns
+    (the call stages a private copy on the caller's stream). Checked with an overwrite queued
+    immediately behind the call, a slow rank so that the transfer starts late, many rounds."""
+    dev = torch.device("cuda", rank)
+    g = UlyssesGroup(device=dev)
+    x = torch.empty(1, 2048, 2 * world, 128, device=dev, dtype=torch.bfloat16)
+    bad = 0
+    for i in range(30):
+        v = float(i + 1)
+        x.fill_(v)
+        if rank == i % world:
+            torch.cuda._sleep(1_000_000)
+        h = g.all_to_all_4d_async(x)
+        x.fill_(-7.0)  # the next writer, on the caller's stream, right behind the call
+        bad += int(not bool(torch.all(h.wait() == v)))
+    g.check()
+    g.destroy()
+    assert bad == 0, f"{bad} results saw the overwrite of x"
+
+
+def pooled_result_read_on_a_side_stream(rank, world):
+    """A pooled result (the default return of all_to_all_4d) read on a side stream: record_stream()
+    does nothing for it, the documented rule is to order the side stream before dropping the
+    tensor. With that rule followed the read is never torn, whatever the next calls do."""
+    dev = torch.device("cuda", rank)
+    g = UlyssesGroup(device=dev)
+    cur, side = torch.cuda.current_stream(dev), torch.cuda.Stream(device=dev)
+    x = torch.empty(1, 2048, 2 * world, 128, device=dev, dtype=torch.bfloat16)
+    bad = 0
+    for i in range(24):
+        v = float(i + 1)
+        x.fill_(v)
+        y = g.all_to_all_4d(x)
+        side.wait_stream(cur)
+        with torch.cuda.stream(side):
+            torch.cuda._sleep(1_000_000)
+            snap = y.clone()
+        cur.wait_stream(side)  # the rule: order the reader before the tensor is dropped
+        del y
+        x.fill_(-1.0)
+        for _ in range(3):  # three calls: every pool buffer is handed out again
+            g.all_to_all_4d(x)
+        bad += int(not bool(torch.all(snap == v)))
+    g.check()
+    g.destroy()
+    assert bad == 0, f"{bad} side-stream reads were torn"
 
 
 def subgroups_gpu(rank, world):
+    """Two sequence-parallel groups side by side (a 2-D mesh). Phase 1: each against
+    torch.distributed on its own process group. Phase 2: the two groups go through DIFFERENT
+    sequences of shapes, one of them under a growing skew, with empty_output() inside the loop;
+    they share nothing, so neither may wait for or disturb the other, and each group's phase
+    counter must end at exactly two per call."""
     tp = 2
     sp = world // tp
     groups = [dist.new_group(list(range(t, world, tp))) for t in range(tp)]
-    mine = groups[rank % tp]
+    which = rank % tp
+    mine = groups[which]
     dev = torch.device("cuda", rank)
     g = UlyssesGroup(mine, device=dev)
     assert g.world_size == sp and g.rank == rank // tp
-    for it in range(10):
-        x = torch.randn(1, 64 + it, 2 * sp, 128, device=dev, dtype=torch.bfloat16)
-        y = g.all_to_all_4d(x)
+
+    def ref(x):
         b, s, n, d = x.shape
         t = x.reshape(b, s, sp, n // sp, d).permute(2, 0, 1, 3, 4).contiguous()
         o = torch.empty_like(t)
         dist.all_to_all_single(o, t, group=mine)
-        assert torch.equal(y, o.permute(1, 0, 2, 3, 4).reshape(b, sp * s, n // sp, d))
+        return o.permute(1, 0, 2, 3, 4).reshape(b, sp * s, n // sp, d)
+
+    for it in range(10):
+        x = torch.randn(1, 64 + it, 2 * sp, 128, device=dev, dtype=torch.bfloat16)
+        assert torch.equal(g.all_to_all_4d(x), ref(x))
+    # phase 2
+    g._handle.set_output_pool(False)  # every call through the window: one phase counter to read
+    shapes = [(1, 48, 2 * sp, 64), (2, 200, 4 * sp, 128), (1, 1000, 2 * sp, 128), (1, 16, 8 * sp, 32)]
+    order = shapes if which == 0 else shapes[::-1]  # opposite orders in the two groups
+    probe = torch.empty(order[0], device=dev, dtype=torch.bfloat16)
+    e0 = g._handle.epoch_debug(probe, 0)
+    calls = 0
+    for it in range(12):
+        shape = order[it % len(order)]
+        x = torch.randn(shape, device=dev, dtype=torch.bfloat16)
+        if which == 1:
+            torch.cuda._sleep(100_000 * (it + 1))  # one group falls further and further behind
+        want = ref(x)
+        assert torch.equal(g.all_to_all_4d(x), want), (which, it, "copying call")
+        calls += 1
+        if it % 3 == 0:
+            out = g.empty_output(x)  # collective inside the loop, on this group only
+            g.all_to_all_4d(x, out=out)
+            assert torch.equal(out, want), (which, it, "zero-copy call")
+    torch.cuda.synchronize()
+    assert g._handle.epoch_debug(probe, 0) == e0 + 2 * calls, "phase counter of the synchronous window"
     g.check()
     g.destroy()
 
@@ -462,6 +631,67 @@ def sp_attention_block(rank, world):
         gsum = p.grad.float().clone()
         dist.all_reduce(gsum)
         assert rel(gsum, r.grad) < 4e-2, (name, rel(gsum, r.grad))
+    g.destroy()
+
+
+def fused_block_beside_an_async_exchange(rank, world):
+    """The fused attention block (persistent kernels whose CTAs wait on peers) while an asynchronous
+    all_to_all_4d of the same group is in flight on the comm stream: both are kernels that wait
+    for the same kernel on other ranks, so both must always fit on the device together. Short
+    time limit: a wait that could not be satisfied would show in check() within half a second."""
+    from fast_ulysses_b200.models.attention import UlyssesSelfAttention
+    from fast_ulysses_b200.ops import gemm
+
+    dev = torch.device("cuda", rank)
+    g = UlyssesGroup(device=dev, timeout_ms=500)
+    grid, hidden, heads = (8, 16, 16 * world), 1024, 8 * world  # 2048 tokens per rank
+    torch.manual_seed(3)
+    attn = UlyssesSelfAttention(g, hidden, heads, grid=grid, timeout_ms=500)
+    x = torch.randn(1, attn.s_local, hidden, device=dev).bfloat16().requires_grad_()
+    payload = torch.randn(1, 8192, 4 * world, 128, device=dev, dtype=torch.bfloat16)  # long enough to overlap
+    want = ref_even(payload, 0, world)
+    bad = 0
+    for i in range(12):
+        if rank == i % world:
+            torch.cuda._sleep(300_000)
+        h = g.all_to_all_4d_async(payload)
+        y = attn(x)
+        y.float().sum().backward()
+        bad += int(not torch.equal(h.wait(), want))
+    torch.cuda.synchronize()
+    gemm.check_errors()
+    g.check()
+    g.destroy()
+    assert bad == 0
+
+
+def fp8_exchange_fused(rank, world):
+    """The one-kernel block-scaled fp8 exchange against its unfused composition (quantise kernel,
+    byte exchange, dequantise kernel): identical bits, both modes, even shards and the uneven
+    shards of a 40-head model (head splits as even as the world allows, sequence shards drawn
+    within 10 % of even from a seed every rank shares)."""
+    import random
+
+    from fast_ulysses_b200.ops import fp8
+
+    dev = torch.device("cuda", rank)
+    g = UlyssesGroup(device=dev)
+    rng = random.Random(2024)
+    heads = [40 // world + (1 if p < 40 % world else 0) for p in range(world)]
+    base = 600
+    seq = [base + rng.randint(-base // 10, base // 10) for _ in range(world)]
+    torch.manual_seed(9 + rank)
+    cases = [((1, 256, 2 * world, 128), 0, None, None), ((2, 64 * world, 3, 128), 1, None, None),
+             ((1, seq[rank], 40, 128), 0, seq, heads), ((1, sum(seq), heads[rank], 128), 1, seq, heads)]
+    for shape, mode, ss, hs in cases * 2:  # twice: the window is reused, the handshakes keep the calls apart
+        x = (torch.randn(shape, device=dev) * 4).bfloat16()
+        fused = fp8.all_to_all_4d_fp8(g, x, mode=mode, seq_splits=ss, head_splits=hs)
+        plain = fp8.all_to_all_4d_fp8(g, x, mode=mode, seq_splits=ss, head_splits=hs, fused=False)
+        assert torch.equal(fused, plain), (shape, mode)
+        exact = g.all_to_all_4d(x, mode=mode, seq_splits=ss, head_splits=hs)
+        amax = exact.float().abs().amax(-1, keepdim=True).clamp_min(1e-30)
+        assert ((fused.float() - exact.float()).abs() / amax).max() < 0.07  # e4m3: three mantissa bits
+    g.check()
     g.destroy()
 
 

@@ -51,3 +51,16 @@ def test_collect_and_bench_a2a_parse_their_arguments():
         r = subprocess.run([sys.executable, os.path.join(ROOT, "benchmarks", script), arg], capture_output=True,
                            text=True, timeout=120)
         assert r.returncode == 0 and "usage" in r.stdout.lower(), r.stderr[-500:]
+
+
+def test_preflight_refuses_a_machine_without_gpus_and_explains_itself(tmp_path):
+    """preflight.py is the manual release gate; without GPUs it must say so instead of running suites."""
+    path = tmp_path / "nvidia-smi"
+    path.write_text("#!/bin/sh\nexit 0\n")  # reports no GPU at all
+    path.chmod(path.stat().st_mode | stat.S_IEXEC)
+    env = {**os.environ, "PATH": f"{tmp_path}:{os.environ['PATH']}"}
+    script = os.path.join(ROOT, "benchmarks", "preflight.py")
+    r = subprocess.run([sys.executable, script], env=env, capture_output=True, text=True, timeout=120)
+    assert r.returncode == 2 and "needs a machine with GPUs" in r.stdout
+    h = subprocess.run([sys.executable, script, "--help"], capture_output=True, text=True, timeout=120)
+    assert h.returncode == 0 and "exclusive.py" in h.stdout and "doctor" in h.stdout

@@ -140,3 +140,39 @@ def test_pull_with_a_buffer_that_is_too_small_is_refused(field, text):
     setattr(q, field, getattr(q, field) - 1)
     assert ck.lib().fu_pull_outproj_check(C.byref(q)) != 0
     assert text in last_error()
+
+
+def test_pull_of_the_gradients_past_a_peer_buffer_is_refused():
+    a = ck.FuPullGradsArgs()
+    head_splits, s_local, s_total = (2, 3), 10, 30
+    a.y = a.dy = a.rope = a.gamma_q = a.gamma_k = BASE
+    a.m, a.s_local, a.seq_off, a.s_total, a.ld_y, a.ld_dy = s_local, s_local, 20, s_total, 1280, 1920
+    a.heads, a.rank, a.world = sum(head_splits), 0, 2
+    for p, h in enumerate(head_splits):
+        a.head_splits[p] = h
+        a.peer_dq[p] = a.peer_dk[p] = a.peer_dv[p] = a.peer_ctrl[p] = BASE + (p + 1) * (1 << 30)
+    a.src_bytes = s_total * max(head_splits) * 256
+    assert ck.lib().fu_pull_qkv_grads_check(C.byref(a)) == 0, last_error()
+    a.src_bytes -= 256
+    assert ck.lib().fu_pull_qkv_grads_check(C.byref(a)) != 0 and "loads from rank 1 reach byte" in last_error()
+    a.src_bytes += 256
+    a.seq_off = 21
+    assert ck.lib().fu_pull_qkv_grads_check(C.byref(a)) != 0 and "do not lie inside a sequence of 30" in last_error()
+
+
+def test_fp8_exchange_route_past_the_packed_window_is_refused():
+    a = ck.FuA2AFp8Args()
+    a.src, a.out = BASE, BASE + (1 << 40)
+    a.rank, a.world, a.n_routes = 0, 2, 2
+    rows, heads = 8, 2                      # 8 tokens x 2 heads per peer, rows of 256 bytes
+    for p in range(2):
+        a.peer_win[p] = a.peer_ctrl[p] = BASE + (p + 1) * (1 << 30)
+        a.routes[p] = ck.FuRoute(p, 0, p * heads * 256, 0, 2 * heads * 256, heads * 256, heads * 256, rows, 1, 0, 0)
+    a.src_bytes, a.out_rows = rows * 2 * heads * 256, 2 * rows * heads
+    a.win_bytes = 2 * rows * heads * 144    # both ranks' shares, packed
+    assert ck.lib().fu_a2a4d_fp8_check(C.byref(a)) == 0, last_error()
+    a.routes[1].dst_off = 2 * rows * heads * 256 - 256  # the last row of the window, then seven more
+    assert ck.lib().fu_a2a4d_fp8_check(C.byref(a)) != 0 and "window of" in last_error()
+    a.routes[1].dst_off = 0
+    a.routes[0].row_bytes = 384             # not whole 128-value rows
+    assert ck.lib().fu_a2a4d_fp8_check(C.byref(a)) != 0 and "whole 128-value rows" in last_error()

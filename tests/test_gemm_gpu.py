@@ -101,3 +101,41 @@ def test_operands_given_with_the_contraction_along_their_rows(m, n, k, a_km, b_k
     got = gemm.gemm_bf16(a.t().contiguous() if a_km else a, b.t().contiguous() if b_kn else b, a_km=a_km, b_kn=b_kn)
     gemm.check_errors()
     assert rel_err(got, want) < 5e-3
+
+
+def test_feed_forward_epilogues_match_pytorch():
+    """GELU forward in the first GEMM's epilogue (which also stores the pre-activation), its
+    derivative in the epilogue of the GEMM that produces its incoming gradient, bias and residual in
+    epilogues: against the same feed-forward in fp32 PyTorch, values and all five gradients."""
+    torch.manual_seed(3)
+    m, hidden, ffn = 300, 256, 520
+    x = torch.randn(2, m // 2, hidden, device="cuda").bfloat16().requires_grad_()
+    res = torch.randn(2, m // 2, hidden, device="cuda").bfloat16().requires_grad_()
+    w1 = (torch.randn(ffn, hidden, device="cuda") * 0.06).bfloat16().requires_grad_()
+    b1 = (torch.randn(ffn, device="cuda") * 0.1).bfloat16().requires_grad_()
+    w2 = (torch.randn(hidden, ffn, device="cuda") * 0.06).bfloat16().requires_grad_()
+    b2 = (torch.randn(hidden, device="cuda") * 0.1).bfloat16().requires_grad_()
+    y = gemm.feed_forward(x, w1, b1, w2, b2, residual=res)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    gemm.check_errors()
+    ref = [t.detach().float().requires_grad_() for t in (x, w1, b1, w2, b2, res)]
+    h = torch.nn.functional.gelu(torch.nn.functional.linear(ref[0], ref[1], ref[2]), approximate="tanh")
+    yr = torch.nn.functional.linear(h, ref[3], ref[4]) + ref[5]
+    yr.backward(dy.float())
+    assert rel_err(y, yr) < 1e-2, rel_err(y, yr)
+    for name, got, want in zip(("x", "w1", "b1", "w2", "b2", "residual"), (x, w1, b1, w2, b2, res), ref):
+        assert rel_err(got.grad, want.grad) < 2.5e-2, (name, rel_err(got.grad, want.grad))
+
+
+def test_linear_with_residual_in_the_epilogue():
+    torch.manual_seed(4)
+    x = torch.randn(130, 192, device="cuda").bfloat16().requires_grad_()
+    w = (torch.randn(264, 192, device="cuda") * 0.07).bfloat16().requires_grad_()
+    r = torch.randn(130, 264, device="cuda").bfloat16().requires_grad_()
+    y = gemm.linear(x, w, None, residual=r)
+    y.backward(torch.ones_like(y))
+    gemm.check_errors()
+    want = x.detach().float() @ w.detach().float().t() + r.detach().float()
+    assert rel_err(y, want) < 1e-2
+    assert torch.equal(r.grad, torch.ones_like(r))

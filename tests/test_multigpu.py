@@ -52,7 +52,7 @@ def test_graph_replay(world):
 
 @pytest.mark.parametrize("world", world_sizes()[:1])
 def test_sync_async_coexist(world):
-    run_ranks(world, "_gpu_workers", "sync_async_coexist", backend="nccl", timeout=300)
+    run_ranks(world, "_gpu_workers", "sync_async_coexist", backend="nccl", timeout=600)
 
 
 @pytest.mark.parametrize("world", world_sizes())
@@ -63,6 +63,16 @@ def test_output_pool(world):
 @pytest.mark.parametrize("world", world_sizes()[:1])
 def test_window_reuse_race(world):
     run_ranks(world, "_gpu_workers", "window_reuse_race", backend="nccl", timeout=300)
+
+
+@pytest.mark.parametrize("world", world_sizes()[:1])
+def test_async_input_may_be_overwritten(world):
+    run_ranks(world, "_gpu_workers", "async_input_may_be_overwritten", backend="nccl", timeout=300)
+
+
+@pytest.mark.parametrize("world", world_sizes()[:1])
+def test_pooled_result_read_on_a_side_stream(world):
+    run_ranks(world, "_gpu_workers", "pooled_result_read_on_a_side_stream", backend="nccl", timeout=300)
 
 
 def test_subgroups():
@@ -80,6 +90,16 @@ def test_peer_timeout_is_reported(world):
 @pytest.mark.parametrize("world", world_sizes())
 def test_sp_attention_block(world):
     run_ranks(world, "_gpu_workers", "sp_attention_block", backend="nccl", timeout=300)
+
+
+@pytest.mark.parametrize("world", world_sizes()[:1])
+def test_fused_block_beside_an_async_exchange(world):
+    run_ranks(world, "_gpu_workers", "fused_block_beside_an_async_exchange", backend="nccl", timeout=300)
+
+
+@pytest.mark.parametrize("world", world_sizes())
+def test_fp8_exchange_fused(world):
+    run_ranks(world, "_gpu_workers", "fp8_exchange_fused", backend="nccl", timeout=300)
 
 
 @pytest.mark.parametrize("world", world_sizes()[:1])

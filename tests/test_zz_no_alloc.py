@@ -64,3 +64,10 @@ def test_no_alloc_backward_refuses_what_does_not_fit():
     a = _args(q, q, q, q, lse, q, q, q, q)
     rc = fn(C.byref(a), ck.stream_ptr())
     assert rc != 0 and b"16384" in lib.fu_last_error()
+    # the second limit: statistics are padded to 128 rows per (batch, head), so 1024 heads of one
+    # row each (1024 rows, far below the first limit) do not fit either, and the message says which
+    q = torch.empty(1, 1, 1024, 128, device="cuda", dtype=torch.bfloat16)
+    lse = torch.empty(1, 1024, 1, device="cuda")
+    a = _args(q, q, q, q, lse, q, q, q, q)
+    rc = fn(C.byref(a), ck.stream_ptr())
+    assert rc != 0 and b"65536" in lib.fu_last_error() and b"roundup" in lib.fu_last_error()
