@@ -19,8 +19,12 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 
 def _time(fn, warm=2, reps=2):
-    for _ in range(warm):
+    from fast_ulysses_b200.ops import gemm as _gemm
+
+    for i in range(warm):
         fn()
+        if i == 0:
+            _gemm.check_errors()  # a kernel that gave up on a wait takes seconds per launch: stop before looping
     torch.cuda.synchronize()
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ms = 0.0

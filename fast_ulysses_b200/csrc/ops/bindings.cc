@@ -66,6 +66,10 @@ struct Prepared {
     Window*     window        = nullptr;
     bool        out_is_window = false;
     int         pool_slot     = 0;  // > 0: `output` is that buffer of the output pool
+    // Every rank evaluates the same condition (role, no out=, pool switched on, no capture): when it
+    // holds, any rank may ask for this call's payload in one of its pool buffers; when it does not,
+    // no rank can, and the kernel is told that there is no pool at all.
+    bool        pool_possible = false;
 };
 
 // The kernel reads a view in place when only the batch and sequence strides are irregular.
@@ -152,7 +156,8 @@ Prepared prepare(Group& g, const at::Tensor& input, int64_t mode, const Splits& 
                 // The result is born in a pooled symmetric buffer that the peers write directly
                 // (this rank tells them which one in the opening handshake). When every buffer is
                 // still referenced by a live tensor, this rank alone falls back to window + copy-out.
-                p.pool_slot = g.take_pool_slot(window_bytes, cur);
+                p.pool_possible = true;
+                p.pool_slot     = g.take_pool_slot(window_bytes, cur);
                 if (p.pool_slot > 0) {
                     // the buffer is marked busy from here; only the tensor's deleter clears the mark,
                     // so a failure before the tensor exists must clear it by hand
@@ -210,7 +215,7 @@ void run_prepared(Group& g, Prepared& p, cudaStream_t stream, int extra_flags)
                                                   + (p.x.size(2) - 1) * p.x.stride(2) + p.x.size(3))
                                                      * elem;
     g.launch(*p.plan, p.x.data_ptr(), src_bytes, *p.window, p.out_is_window ? nullptr : p.output.data_ptr(),
-             p.out_is_window ? 0 : out_bytes, stream, extra_flags, p.pool_slot);
+             p.out_is_window ? 0 : out_bytes, stream, extra_flags, p.pool_slot, p.pool_possible);
 }
 
 cudaStream_t current_stream(const Group& g)

@@ -395,7 +395,7 @@ void Group::prune_owned()
 }
 
 void Group::launch(const Plan& plan, const void* src, int64_t src_bytes, const Window& w, void* out,
-                   int64_t out_bytes, void* stream, int extra_flags, int pool_slot)
+                   int64_t out_bytes, void* stream, int extra_flags, int pool_slot, bool pool_possible)
 {
     FuA2AArgs a{};
     a.src        = src;
@@ -403,9 +403,13 @@ void Group::launch(const Plan& plan, const void* src, int64_t src_bytes, const W
     a.win_bytes  = w.capacity;
     a.pool_bytes = pool_capacity_;
     // Every rank passes the whole pool, whatever it chose itself: a peer may have chosen any buffer.
-    a.n_pool  = static_cast<int32_t>(pool_.size());
+    // A call that cannot use the pool on any rank (asynchronous, out=, captured, pool switched off)
+    // passes none: the kernel then ignores whatever a control block still says from an earlier call.
+    TORCH_INTERNAL_ASSERT(pool_possible || pool_slot == 0);
+    const size_t n_pool = pool_possible ? pool_.size() : 0;
+    a.n_pool  = static_cast<int32_t>(n_pool);
     a.my_slot = pool_slot;
-    for (size_t k = 0; k < pool_.size(); ++k) {
+    for (size_t k = 0; k < n_pool; ++k) {
         for (int p = 0; p < world_; ++p) {
             a.peer_pool[p][k] = pool_[k].w->base[static_cast<size_t>(p)];
         }

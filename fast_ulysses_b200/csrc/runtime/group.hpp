@@ -101,8 +101,9 @@ public:
     // Launch on `stream`. `out` may be null (result stays in the window). `src_bytes` is the extent
     // of the input behind `src`; with the capacities of the window and the pool it lets the launcher
     // refuse a route that would leave its buffer.
+    // `pool_possible`: some rank may have chosen a pool buffer for this call (the same on every rank).
     void launch(const Plan& plan, const void* src, int64_t src_bytes, const Window& w, void* out, int64_t out_bytes,
-                void* stream, int extra_flags, int pool_slot = 0);
+                void* stream, int extra_flags, int pool_slot = 0, bool pool_possible = false);
     void barrier(Role role, void* stream);
 
     // CPU/gloo execution of the same plan.

@@ -32,6 +32,11 @@ def bench_attention_block(group, world: int, rank: int, time_steps, flush, steps
                       "per_rank_x": [1, s_local, HIDDEN], "kernels": "fused qkv+norm+rope+scatter, tcgen05 fmha, "
                       "pull+outproj; backward: scatter-epilogue dgrad, tcgen05 fmha bwd, fused pull of dq/dk/dv + "
                       "norm/rope backward, tcgen05 dgrad/wgrad"}}
+    # one step, then look at the error words before anything is looped: a kernel that gives up on an
+    # internal wait takes seconds per launch, and a timing loop would multiply that
+    step()
+    gemm.check_errors()
+    group.check()
     out["fwd_ms"] = time_steps(fwd, steps, warmup, world, flush)
     out["fwd_bwd_ms"] = time_steps(step, steps, warmup, world, flush)
     gemm.check_errors()
