@@ -34,7 +34,7 @@ constexpr int      kAhead       = kStages - 2;  // loads issued this many chunks
 constexpr int      kLdstThreads = 512;
 constexpr int      kLdstUnroll  = 8;           // 16-byte loads in flight per thread
 constexpr int      kLdstChunkBytes = 64 * 1024;  // = threads x unroll x 16 B: one pass per chunk
-constexpr int      kLdstCtasPerSm  = 2;
+constexpr int      kLdstCtasPerSm  = 1;           // 128 registers per thread: eight 16-byte vectors in flight without spilling
 constexpr uint32_t kDefaultTimeoutMs = 10000;
 
 // A route plus its decomposition into chunks of at most one stage.
@@ -144,8 +144,10 @@ struct ChunkCursor {
 
 // ---- data movers ------------------------------------------------------------------------------------
 struct BulkPipe {
-    uint8_t*  stage[kStages];
+    uint8_t*  base;  // kStages buffers of kStageBytes each (an address computed, not an array indexed
+                     // at run time: that would live in local memory)
     uint64_t* full;  // kStages mbarriers
+    __device__ __forceinline__ uint8_t* stage(int s) const { return base + s * kStageBytes; }
 };
 
 __device__ __forceinline__ void bulk_issue_loads(const BulkPipe& p, int s, const Chunk& c, int lane)
@@ -157,12 +159,12 @@ __device__ __forceinline__ void bulk_issue_loads(const BulkPipe& p, int s, const
     __syncwarp();
     if (c.src_pitch == c.row_bytes) {
         if (lane == 0) {
-            bulk_g2s(p.stage[s], c.src, total, &p.full[s]);
+            bulk_g2s(p.stage(s), c.src, total, &p.full[s]);
         }
     }
     else {
         for (uint32_t r = lane; r < c.nrows; r += 32) {
-            bulk_g2s(p.stage[s] + r * c.row_bytes, c.src + r * c.src_pitch, c.row_bytes, &p.full[s]);
+            bulk_g2s(p.stage(s) + r * c.row_bytes, c.src + r * c.src_pitch, c.row_bytes, &p.full[s]);
         }
     }
 }
@@ -171,12 +173,12 @@ __device__ __forceinline__ void bulk_issue_stores(const BulkPipe& p, int s, cons
 {
     if (c.dst_pitch == c.row_bytes) {
         if (lane == 0) {
-            bulk_s2g(c.dst, p.stage[s], c.nrows * c.row_bytes);
+            bulk_s2g(c.dst, p.stage(s), c.nrows * c.row_bytes);
         }
     }
     else {
         for (uint32_t r = lane; r < c.nrows; r += 32) {
-            bulk_s2g(c.dst + r * c.dst_pitch, p.stage[s] + r * c.row_bytes, c.row_bytes);
+            bulk_s2g(c.dst + r * c.dst_pitch, p.stage(s) + r * c.row_bytes, c.row_bytes);
         }
     }
     bulk_commit();  // every lane commits one (possibly empty) group per chunk
@@ -242,8 +244,9 @@ __device__ void ldst_move(const RouteSet& set, const int64_t* shift = nullptr)
         const uint32_t vpr  = c.row_bytes >> 4;
         const uint32_t nvec = vpr * c.nrows;
         for (uint32_t v0 = threadIdx.x; v0 < nvec; v0 += kLdstUnroll * kLdstThreads) {
-            uint4    val[kLdstUnroll];
-            uint8_t* dst[kLdstUnroll];
+            // only the data stays in registers between the loads and the stores: the destination of
+            // each vector is recomputed (two integer divisions are cheaper than 16 spilled registers)
+            uint4 val[kLdstUnroll];
 #pragma unroll
             for (int u = 0; u < kLdstUnroll; ++u) {
                 const uint32_t v = v0 + u * kLdstThreads;
@@ -252,13 +255,15 @@ __device__ void ldst_move(const RouteSet& set, const int64_t* shift = nullptr)
                     const uint32_t col = v - row * vpr;
                     const uint8_t* from = c.src + row * c.src_pitch + (static_cast<int64_t>(col) << 4);
                     val[u]             = kCoherent ? ld_v4(from) : ld_nc_v4(from);
-                    dst[u]             = c.dst + row * c.dst_pitch + (static_cast<int64_t>(col) << 4);
                 }
             }
 #pragma unroll
             for (int u = 0; u < kLdstUnroll; ++u) {
-                if (v0 + u * kLdstThreads < nvec) {
-                    st_v4(dst[u], val[u]);
+                const uint32_t v = v0 + u * kLdstThreads;
+                if (v < nvec) {
+                    const uint32_t row = v / vpr;
+                    const uint32_t col = v - row * vpr;
+                    st_v4(c.dst + row * c.dst_pitch + (static_cast<int64_t>(col) << 4), val[u]);
                 }
             }
         }
@@ -282,9 +287,7 @@ __global__ void __launch_bounds__(kBulk ? 32 : kLdstThreads, kBulk ? 1 : kLdstCt
 
     BulkPipe pipe;
     if (kBulk) {
-        for (int s = 0; s < kStages; ++s) {
-            pipe.stage[s] = smem + s * kStageBytes;
-        }
+        pipe.base = smem;
         pipe.full = full_bar;
         if (threadIdx.x == 0) {
             for (int s = 0; s < kStages; ++s) {

@@ -32,10 +32,13 @@ def _fill(a, q, k, v, o):
 
 
 def fmha_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scale: float | None = None,
-             out: torch.Tensor | None = None, ctas: int = 0, poly: int | None = None):
+             out: torch.Tensor | None = None, ctas: int = 0, poly: int | None = None,
+             trace: torch.Tensor | None = None):
     """``softmax(q k^T * scale) v`` for (b, s, h, 128) bf16 tensors. Returns ``(o, lse)`` with
     ``lse`` of shape (b, h, s_q), fp32, natural log. ``poly`` (0, 2, 4 or 6) overrides how many of
-    every 16 exponential pairs are computed on the FMA pipe instead of the special-function unit."""
+    every 16 exponential pairs are computed on the FMA pipe instead of the special-function unit.
+    ``trace`` (int64[256] on the device) selects the instrumented build of the kernel: CTA 0 stores the
+    SM clock of 32 pipeline events for kv steps 64..71 of its first item."""
     b, sq, h, d = q.shape
     assert k.shape == v.shape and k.shape[0] == b and k.shape[2] == h and d == 128
     o = out if out is not None else torch.empty(b, sq, h, d, dtype=torch.bfloat16, device=q.device)
@@ -47,6 +50,9 @@ def fmha_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scale: float 
     a.ctas = ctas
     if poly is not None:
         a.flags = 0x1000 | ((poly & 15) << 8)  # FU_FMHA_POLY(poly)
+    if trace is not None:
+        assert trace.dtype == torch.int64 and trace.numel() >= 256 and trace.is_cuda
+        a.trace = trace.data_ptr()
     ck.check(ck.lib().fu_fmha_fwd(C.byref(a), ck.stream_ptr()))
     return o, lse
 
