@@ -537,6 +537,9 @@ def subgroups_gpu(rank, world):
     g._handle.set_output_pool(False)  # every call through the window: one phase counter to read
     shapes = [(1, 48, 2 * sp, 64), (2, 200, 4 * sp, 128), (1, 1000, 2 * sp, 128), (1, 16, 8 * sp, 32)]
     order = shapes if which == 0 else shapes[::-1]  # opposite orders in the two groups
+    # the largest shape first: a window that grows is a new window, whose counter starts again at zero
+    g.all_to_all_4d(torch.zeros(max(shapes, key=lambda sh: sh[0] * sh[1] * sh[2] * sh[3]), device=dev,
+                                dtype=torch.bfloat16))
     probe = torch.empty(order[0], device=dev, dtype=torch.bfloat16)
     e0 = g._handle.epoch_debug(probe, 0)
     calls = 0
