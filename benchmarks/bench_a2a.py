@@ -7,9 +7,10 @@ Modes follow the reference's benchmark/bench_a2a.py:168-443 (stages, zerocopy, p
 overlap, link). `link` is the ceiling every NVLink fraction in this repository is quoted against:
 flat 64 MiB copies from rank r into rank (r+1) % N's memory through this library's own two data
 paths (bulk copies, and 16-byte loads and stores), one flow and all N flows at once, with no
-handshake and no relayout. `overlap` also reports how much the GEMMs slow down while the exchange
-runs beside them: an exchange on the SMs can hide itself by taking time from them. The reference's
-`zerosm` mode measured its copy engines, which this library does not use.
+handshake and no relayout. `overlap` runs once per transport of the asynchronous call (the kernel, and
+the copy engines) and also reports how much the GEMMs slow down while the exchange runs beside
+them: an exchange on the SMs can hide itself by taking time from them, which is the question the
+reference's `zerosm` mode (:446-637) asked of its copy engines.
 BASE is the torch.distributed form (permute, all_to_all_single, permute). Every number is a CUDA
 event time, L2 flushed between iterations, the maximum over ranks; rank 0 prints one JSON line
 per measurement.
@@ -118,19 +119,23 @@ def main():
             for _ in range(3):
                 a @ a
 
+        # `x` is never written here, so the asynchronous call reads it in place (stage=False)
+        def alone():
+            g.all_to_all_4d_async(x, stage=False).wait()
+
         def serial():
             gemms()
-            g.all_to_all_4d(x)
+            g.all_to_all_4d_async(x, stage=False).wait()
 
         def concurrent():
-            h = g.all_to_all_4d_async(x)
+            h = g.all_to_all_4d_async(x, stage=False)
             gemms()
             h.wait()
 
         # how long the GEMMs themselves take while the exchange runs beside them (events around the
-        # GEMMs only, on the caller's stream)
+        # GEMMs only, on the caller's stream): an exchange can hide itself by taking SMs from them
         def gemms_beside():
-            h = g.all_to_all_4d_async(x)
+            h = g.all_to_all_4d_async(x, stage=False)
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
             gemms()
@@ -138,19 +143,22 @@ def main():
             h.wait()
             return e0, e1
 
-        t_g, t_a = run(gemms, args.iters), run(lambda: g.all_to_all_4d(x), args.iters)
-        t_s, t_c = run(serial, args.iters), run(concurrent, args.iters)
-        pairs = []
-        for _ in range(args.iters):
-            flush.zero_()
-            pairs.append(gemms_beside())
-        torch.cuda.synchronize()
-        beside = sorted(a.elapsed_time(b) for a, b in pairs)[len(pairs) // 2]
-        tb = torch.tensor([beside], device="cuda", dtype=torch.float64)
-        dist.all_reduce(tb, op=dist.ReduceOp.MAX)
-        emit(rank, mode="overlap", shape=args.shape, world=world, gemm_ms=t_g, a2a_ms=t_a, serial_ms=t_s,
-             concurrent_ms=t_c, hidden_pct=100.0 * (t_s - t_c) / t_a, gemm_beside_exchange_ms=float(tb),
-             gemm_slowdown_pct=100.0 * (float(tb) - t_g) / t_g)
+        t_g = run(gemms, args.iters)
+        for transport in ("kernel", "copy_engine"):
+            g.set_async_transport(transport)
+            t_a = run(alone, args.iters)
+            t_s, t_c = run(serial, args.iters), run(concurrent, args.iters)
+            pairs = []
+            for _ in range(args.iters):
+                flush.zero_()
+                pairs.append(gemms_beside())
+            torch.cuda.synchronize()
+            beside = sorted(a.elapsed_time(b) for a, b in pairs)[len(pairs) // 2]
+            tb = torch.tensor([beside], device="cuda", dtype=torch.float64)
+            dist.all_reduce(tb, op=dist.ReduceOp.MAX)
+            emit(rank, mode="overlap", transport=transport, shape=args.shape, world=world, gemm_ms=t_g, a2a_ms=t_a,
+                 serial_ms=t_s, concurrent_ms=t_c, hidden_pct=100.0 * (t_s - t_c) / t_a,
+                 gemm_beside_exchange_ms=float(tb), gemm_slowdown_pct=100.0 * (float(tb) - t_g) / t_g)
     elif args.mode == "fp8":
         from fast_ulysses_b200.ops import fp8
 

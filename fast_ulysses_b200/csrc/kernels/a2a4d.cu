@@ -15,6 +15,11 @@
 // output buffers (then nothing is copied out afterwards). The choice travels with the opening
 // announcement (FuCtrl::slot_of) and every sender shifts its routes to that rank accordingly, so
 // ranks with different numbers of live results need not agree on anything.
+//
+// A second transport, chosen per launch (FU_A2A_COPY_ENGINE), moves the same routes with the copy
+// engines between two one-warp handshake kernels (the reference's data plane, src/transfer.cu:26-52):
+// slower to start, but it holds no SM while the payload moves, which is what a call that runs beside
+// GEMMs wants. Both transports speak the same handshake, so ranks may mix them.
 #include "fu_kernels.h"
 #include "handshake.cuh"
 #include "host_util.h"
@@ -432,6 +437,46 @@ __global__ void __launch_bounds__(32, 1)
     }
 }
 
+// The two handshakes of the copy-engine transport, one warp each. Phase 1 opens (announce "my reads
+// of my window are finished", wait for every rank's); phase 2 runs after the copies in stream order
+// and closes (announce "my writes have landed", wait for every rank's, advance the phase counter).
+// A copy that precedes this kernel in its stream has completed, destination writes included, before
+// the kernel starts; the system-scope fence and the release on the flags order it for the peers.
+__global__ void __launch_bounds__(32, 1) ce_phase_kernel(const __grid_constant__ fu::Peers p, int phase, int flags)
+{
+    FuCtrl*        own    = p.own;
+    const uint64_t base   = *reinterpret_cast<volatile uint64_t*>(&own->epoch);
+    const bool     stamps = (flags & FU_A2A_STAMPS) && threadIdx.x == 0;
+    if (phase == 1) {
+        if (stamps) {
+            own->stamps[0] = globaltimer_ns();
+        }
+        fu::hs_announce(p, base + 1, 0);  // buffer 0: this call's payload goes to the window
+        if (flags & FU_A2A_EARLY_PUBLISH) {
+            fu::hs_announce(p, base + 2);
+        }
+        fu::hs_await(p, base + 1, FU_ST_OPEN_TIMEOUT);
+        if (stamps) {
+            own->stamps[1] = globaltimer_ns();
+        }
+        return;
+    }
+    if (stamps) {
+        own->stamps[2] = globaltimer_ns();
+    }
+    fence_sys();
+    fu::hs_announce(p, base + 2);
+    fu::hs_await(p, base + 2, FU_ST_CLOSE_TIMEOUT);
+    __syncwarp();
+    if (threadIdx.x == 0) {
+        if (flags & FU_A2A_STAMPS) {
+            own->stamps[3] = own->stamps[4] = globaltimer_ns();
+        }
+        __threadfence();
+        *reinterpret_cast<volatile uint64_t*>(&own->epoch) = base + 2;
+    }
+}
+
 // ---- host side ----------------------------------------------------------------------------------------
 // Cuts a route into chunks of at most `chunk` bytes. A route that is dense on both sides is first
 // folded into one long row, so that its chunks are large whatever the row length was.
@@ -557,6 +602,10 @@ int build_args(const FuA2AArgs* args, KArgs& k)
     }
     if (in.n_pool < 0 || in.n_pool > FU_POOL_SLOTS || in.my_slot < 0 || in.my_slot > in.n_pool) {
         return fu::fail(FU_E_ARG, "fu_a2a4d: pool buffer %d of %d", in.my_slot, in.n_pool);
+    }
+    if ((in.flags & FU_A2A_COPY_ENGINE) && in.n_pool > 0) {
+        return fu::fail(FU_E_ARG, "fu_a2a4d: the copy-engine transport cannot serve a call that may use the output "
+                                  "pool (which buffer a peer chose is known on the device only)");
     }
     k.n_pool  = in.n_pool;
     k.my_slot = in.my_slot;
@@ -698,6 +747,74 @@ int build_args(const FuA2AArgs* args, KArgs& k)
 
 }  // namespace
 
+namespace {
+
+// One route on the copy engines: a pitched copy per batch (a flat one where both sides are dense).
+int copy_route(const FuRoute& r, const uint8_t* src_base, uint8_t* dst_base, cudaStream_t stream)
+{
+    if (r.rows <= 0 || r.batches <= 0 || r.row_bytes <= 0) {
+        return FU_OK;
+    }
+    for (int64_t b = 0; b < r.batches; ++b) {
+        const uint8_t* s = src_base + r.src_off + b * r.src_batch;
+        uint8_t*       d = dst_base + r.dst_off + b * r.dst_batch;
+        if (r.rows == 1 || (r.src_pitch == r.row_bytes && r.dst_pitch == r.row_bytes)) {
+            FU_CUDA_OK(cudaMemcpyAsync(d, s, static_cast<size_t>(r.row_bytes * r.rows), cudaMemcpyDeviceToDevice, stream));
+        }
+        else {
+            FU_CUDA_OK(cudaMemcpy2DAsync(d, static_cast<size_t>(r.dst_pitch), s, static_cast<size_t>(r.src_pitch),
+                                         static_cast<size_t>(r.row_bytes), static_cast<size_t>(r.rows),
+                                         cudaMemcpyDeviceToDevice, stream));
+        }
+    }
+    return FU_OK;
+}
+
+// The whole call on the copy engines. `in` has passed build_args(), so every route lies inside the
+// buffers it names. The routes run one after another on the caller's stream: one copy-engine flow
+// fills a GPU's NVLink egress, so nothing is gained by spreading them over streams, and the order in
+// which `in.routes` lists the peers (next rank up first) keeps every rank's ingress fed by one sender
+// at a time.
+int launch_copy_engine(const FuA2AArgs& in, const KArgs& k, cudaStream_t stream)
+{
+    const bool handshake = !(in.flags & FU_A2A_NO_HANDSHAKE);
+    const bool copy_out  = in.out && in.out_bytes > 0;
+    if (handshake) {
+        ce_phase_kernel<<<1, 32, 0, stream>>>(k.peers, 1, in.flags);
+        FU_CUDA_OK(cudaGetLastError());
+    }
+    for (int i = 0; i < in.n_routes; ++i) {
+        const FuRoute& r      = in.routes[i];
+        const bool     direct = copy_out && in.own_direct && r.peer == in.rank;
+        uint8_t*       dst    = direct ? static_cast<uint8_t*>(in.out) : static_cast<uint8_t*>(in.peer_win[r.peer]);
+        const int      rc     = copy_route(r, static_cast<const uint8_t*>(in.src), dst, stream);
+        if (rc != FU_OK) {
+            return rc;
+        }
+    }
+    if (handshake) {
+        ce_phase_kernel<<<1, 32, 0, stream>>>(k.peers, 2, in.flags);
+        FU_CUDA_OK(cudaGetLastError());
+    }
+    if (copy_out) {
+        const uint8_t* win = static_cast<const uint8_t*>(in.peer_win[in.rank]);
+        if (in.n_out_routes > 0 || in.own_direct) {
+            for (int i = 0; i < in.n_out_routes; ++i) {
+                const int rc = copy_route(in.out_routes[i], win, static_cast<uint8_t*>(in.out), stream);
+                if (rc != FU_OK) {
+                    return rc;
+                }
+            }
+        }
+        else {
+            FU_CUDA_OK(cudaMemcpyAsync(in.out, win, static_cast<size_t>(in.out_bytes), cudaMemcpyDeviceToDevice, stream));
+        }
+    }
+    return FU_OK;
+}
+
+}  // namespace
+
 extern "C" int fu_a2a4d_check(const FuA2AArgs* args)
 {
     KArgs k{};
@@ -714,6 +831,9 @@ extern "C" int fu_a2a4d(const FuA2AArgs* args, void* stream_v)
     const FuA2AArgs& in   = *args;
     const bool       ldst = (in.flags & FU_A2A_LDST) != 0;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    if (in.flags & FU_A2A_COPY_ENGINE) {
+        return launch_copy_engine(in, k, stream);
+    }
     int          dev = 0, sms = 0;
     FU_CUDA_OK(cudaGetDevice(&dev));
     FU_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));

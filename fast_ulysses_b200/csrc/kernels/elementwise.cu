@@ -229,55 +229,83 @@ __global__ void __launch_bounds__(256) pull_qkv_grads_kernel(const __grid_consta
         if (t < 2) {
             gm = *reinterpret_cast<const float4*>(p.gamma[t] + lane * 4);
         }
-        for (int64_t it = warp0; it < items; it += nwarps) {
-            const int64_t  row   = it / p.heads;
-            const int      head  = static_cast<int>(it - row * p.heads);
-            const int64_t  batch = row / p.s_local;
-            const int64_t  s     = row - batch * p.s_local;
-            const int      peer  = p.owner[head];
-            const int64_t  hp    = p.heads_of[peer];
-            const uint8_t* from  = p.src[t][peer] + (((batch * p.s_total + p.seq_off + s) * hp + p.local[head]) * 128 + lane * 4) * 2;
-            uint2 gv;
-            asm volatile("ld.global.v2.u32 {%0, %1}, [%2];" : "=r"(gv.x), "=r"(gv.y) : "l"(from));
-            __nv_bfloat16* to = p.dy + row * p.ld_dy + (static_cast<int64_t>(t) * p.heads + head) * 128 + lane * 4;
-            if (t == 2) {
-                *reinterpret_cast<uint2*>(to) = gv;  // dv needs no transformation
-                continue;
-            }
-            const uint2  yv  = *reinterpret_cast<const uint2*>(p.y + row * p.ld_y + (t * p.heads + head) * 128 + lane * 4);
-            const float2 g01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&gv.x));
-            const float2 g23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&gv.y));
-            const float2 y01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&yv.x));
-            const float2 y23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&yv.y));
-            const float4 cs  = *reinterpret_cast<const float4*>(p.rope + s * 64 + lane * 2);  // (c0, s0, c1, s1)
-            // undo the rotation: the transpose of a rotation is the opposite rotation
-            const float dx[4] = {g01.x * cs.x + g01.y * cs.y, -g01.x * cs.y + g01.y * cs.x,
-                                 g23.x * cs.z + g23.y * cs.w, -g23.x * cs.w + g23.y * cs.z};
-            const float yy[4] = {y01.x, y01.y, y23.x, y23.y};
-            float       ss    = yy[0] * yy[0] + yy[1] * yy[1] + yy[2] * yy[2] + yy[3] * yy[3];
+        // Four rows per warp in flight: a load from a peer takes microseconds, and with one per
+        // warp the kernel would wait on latency instead of on the link.
+        constexpr int kInFlight = 4;
+        for (int64_t it0 = warp0; it0 < items; it0 += nwarps * kInFlight) {
+            uint2   gvs[kInFlight], yvs[kInFlight];
+            int64_t rows[kInFlight];
+            int     hds[kInFlight];
 #pragma unroll
-            for (int off = 16; off > 0; off >>= 1) {
-                ss += __shfl_xor_sync(0xffffffffu, ss, off);
-            }
-            const float rstd   = rsqrtf(ss * (1.0f / 128.0f) + p.eps);
-            const float gmv[4] = {gm.x, gm.y, gm.z, gm.w};
-            float       n[4], dn[4], dot = 0.0f;
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                n[k]  = yy[k] * rstd;
-                dn[k] = dx[k] * gmv[k];
-                dg[k] += dx[k] * n[k];
-                dot += dn[k] * n[k];
+            for (int u = 0; u < kInFlight; ++u) {
+                const int64_t it = it0 + u * nwarps;
+                rows[u]          = -1;
+                if (it < items) {
+                    const int64_t  row   = it / p.heads;
+                    const int      head  = static_cast<int>(it - row * p.heads);
+                    const int64_t  batch = row / p.s_local;
+                    const int64_t  s     = row - batch * p.s_local;
+                    const int      peer  = p.owner[head];
+                    const int64_t  hp    = p.heads_of[peer];
+                    const uint8_t* from  = p.src[t][peer]
+                                          + (((batch * p.s_total + p.seq_off + s) * hp + p.local[head]) * 128 + lane * 4) * 2;
+                    asm volatile("ld.global.v2.u32 {%0, %1}, [%2];" : "=r"(gvs[u].x), "=r"(gvs[u].y) : "l"(from));
+                    if (t < 2) {
+                        yvs[u] = *reinterpret_cast<const uint2*>(p.y + row * p.ld_y + (t * p.heads + head) * 128 + lane * 4);
+                    }
+                    rows[u] = row;
+                    hds[u]  = head;
+                }
             }
 #pragma unroll
-            for (int off = 16; off > 0; off >>= 1) {
-                dot += __shfl_xor_sync(0xffffffffu, dot, off);
+            for (int u = 0; u < kInFlight; ++u) {
+                if (rows[u] < 0) {
+                    continue;
+                }
+                const int64_t row  = rows[u];
+                const int     head = hds[u];
+                const int64_t s    = row % p.s_local;
+                const uint2   gv   = gvs[u];
+                __nv_bfloat16* to = p.dy + row * p.ld_dy + (static_cast<int64_t>(t) * p.heads + head) * 128 + lane * 4;
+                if (t == 2) {
+                    *reinterpret_cast<uint2*>(to) = gv;  // dv needs no transformation
+                    continue;
+                }
+                const uint2  yv  = yvs[u];
+                const float2 g01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&gv.x));
+                const float2 g23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&gv.y));
+                const float2 y01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&yv.x));
+                const float2 y23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&yv.y));
+                const float4 cs  = *reinterpret_cast<const float4*>(p.rope + s * 64 + lane * 2);  // (c0, s0, c1, s1)
+                // undo the rotation: the transpose of a rotation is the opposite rotation
+                const float dx[4] = {g01.x * cs.x + g01.y * cs.y, -g01.x * cs.y + g01.y * cs.x,
+                                     g23.x * cs.z + g23.y * cs.w, -g23.x * cs.w + g23.y * cs.z};
+                const float yy[4] = {y01.x, y01.y, y23.x, y23.y};
+                float       ss    = yy[0] * yy[0] + yy[1] * yy[1] + yy[2] * yy[2] + yy[3] * yy[3];
+#pragma unroll
+                for (int off = 16; off > 0; off >>= 1) {
+                    ss += __shfl_xor_sync(0xffffffffu, ss, off);
+                }
+                const float rstd   = rsqrtf(ss * (1.0f / 128.0f) + p.eps);
+                const float gmv[4] = {gm.x, gm.y, gm.z, gm.w};
+                float       n[4], dn[4], dot = 0.0f;
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    n[k]  = yy[k] * rstd;
+                    dn[k] = dx[k] * gmv[k];
+                    dg[k] += dx[k] * n[k];
+                    dot += dn[k] * n[k];
+                }
+#pragma unroll
+                for (int off = 16; off > 0; off >>= 1) {
+                    dot += __shfl_xor_sync(0xffffffffu, dot, off);
+                }
+                dot *= (1.0f / 128.0f);
+                uint2 out;
+                out.x = fu::ptx::pack_bf16x2(rstd * (dn[0] - n[0] * dot), rstd * (dn[1] - n[1] * dot));
+                out.y = fu::ptx::pack_bf16x2(rstd * (dn[2] - n[2] * dot), rstd * (dn[3] - n[3] * dot));
+                *reinterpret_cast<uint2*>(to) = out;
             }
-            dot *= (1.0f / 128.0f);
-            uint2 out;
-            out.x = fu::ptx::pack_bf16x2(rstd * (dn[0] - n[0] * dot), rstd * (dn[1] - n[1] * dot));
-            out.y = fu::ptx::pack_bf16x2(rstd * (dn[2] - n[2] * dot), rstd * (dn[3] - n[3] * dot));
-            *reinterpret_cast<uint2*>(to) = out;
         }
         if (t < 2 && p.dgamma[t]) {
 #pragma unroll

@@ -63,6 +63,12 @@ enum {
     FU_A2A_MUTE          = 16,  // TEST ONLY: never announce anything, so that peers' waits run out
     FU_A2A_MINOR_SHARE   = 32,  // this launch may run beside another collective of the same rank on
                                 // an unordered stream: take a third of the device, not two thirds
+    FU_A2A_COPY_ENGINE   = 128, // move the payload with the copy engines (one cudaMemcpy2DAsync per
+                                // route and batch) between two one-warp handshake kernels: no SM is
+                                // held while the payload moves, so GEMMs beside the call keep the
+                                // whole device. Same handshake protocol as the kernel transport, so
+                                // ranks may mix the two. Not available to a call that may use the
+                                // output pool (the host cannot know which buffer a peer chose).
 };
 
 // Output pool. A rank may ask its peers, per call, to write into one of up to FU_POOL_SLOTS extra

@@ -276,17 +276,21 @@ struct QkvEpi {
             }
             const float*  gamma = type == 0 ? p.gamma_q : p.gamma_k;
             const float2* cs    = p.rope + (row_ok ? s : 0) * (HEAD_DIM / 2);
+            // The finished head rows (256 bytes each) go through a per-warp staging buffer so that
+            // every store instruction to the owner's window writes whole rows: lanes 0-15 one row,
+            // lanes 16-31 the next. Written straight from the accumulator layout (a lane is a row)
+            // each instruction would scatter 32 separate 16-byte pieces, which NVLink carries at a
+            // fraction of its rate. 16-byte units are XOR-swizzled by the row so that neither the
+            // row-wise writes nor the row-wide reads conflict on shared-memory banks.
+            uint8_t* stage = stage_of(quarter);
 #pragma unroll 1
             for (int chunk = 0; chunk < 4; ++chunk) {
                 uint32_t r[32];
                 ptx::tmem_ld_32x32(tcol + chunk * 32, r);
                 ptx::tmem_ld_wait();
-                if (!row_ok) {
-                    continue;
-                }
                 uint32_t o[16];
                 if (normed) {
-                    if (p.y_save) {
+                    if (p.y_save && row_ok) {
                         uint4* ys = reinterpret_cast<uint4*>(p.y_save + static_cast<int64_t>(row) * p.ld_y
                                                              + head_global * HEAD_DIM + chunk * 32);
 #pragma unroll
@@ -312,13 +316,37 @@ struct QkvEpi {
                         o[i] = pack_bf16(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
                     }
                 }
-                uint4* out = reinterpret_cast<uint4*>(dst + chunk * 64);
 #pragma unroll
                 for (int q4 = 0; q4 < 4; ++q4) {
-                    ptx::st_v4(out + q4, make_uint4(o[4 * q4], o[4 * q4 + 1], o[4 * q4 + 2], o[4 * q4 + 3]));
+                    const int unit = (chunk * 4 + q4) ^ (lane & 15);
+                    *reinterpret_cast<uint4*>(stage + lane * 256 + unit * 16) =
+                        make_uint4(o[4 * q4], o[4 * q4 + 1], o[4 * q4 + 2], o[4 * q4 + 3]);
                 }
             }
+            __syncwarp();
+            const unsigned long long my_dst = row_ok ? reinterpret_cast<unsigned long long>(dst) : 0ull;
+            const int                unit   = lane & 15;
+#pragma unroll 4
+            for (int i = 0; i < 16; ++i) {
+                const int                r_src = 2 * i + (lane >> 4);
+                const unsigned long long to    = __shfl_sync(0xffffffffu, my_dst, r_src);
+                const uint4 v = *reinterpret_cast<const uint4*>(stage + r_src * 256 + ((unit ^ (r_src & 15)) * 16));
+                if (to) {
+                    ptx::st_v4(reinterpret_cast<uint4*>(to) + unit, v);
+                }
+            }
+            __syncwarp();  // the buffer is refilled by the next head
         }
+    }
+
+    // 8 KiB of staging per epilogue warp, behind the operand ring in dynamic shared memory.
+    static constexpr int kStageBytesPerWarp = 32 * HEAD_DIM * 2;
+    static constexpr int kExtraSmem         = 4 * kStageBytesPerWarp;
+    __device__ static uint8_t* stage_of(int quarter)
+    {
+        extern __shared__ uint8_t smem_raw[];
+        const uint32_t base = (ptx::smem_addr(smem_raw) + 1023u) & ~1023u;
+        return smem_raw + (base - ptx::smem_addr(smem_raw)) + STAGES * STAGE_BYTES + quarter * kStageBytesPerWarp;
     }
 };
 
@@ -486,13 +514,13 @@ int launch_grid(int ctas, int tiles)
 }
 
 template <class K>
-int set_smem(K kernel)
+int set_smem(K kernel, int bytes = SMEM_BYTES)
 {
     static bool done[64] = {};
     int         dev      = 0;
     FU_CUDA_OK(cudaGetDevice(&dev));
     if (dev < 64 && !done[dev]) {
-        FU_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        FU_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
         done[dev] = true;
     }
     return FU_OK;
@@ -681,12 +709,12 @@ extern "C" int fu_qkv_rope_scatter(const FuQkvArgs* q, void* stream)
     if (q->y_save && ((q->ld_y % 8) || (reinterpret_cast<uintptr_t>(q->y_save) & 15u))) {
         return fu::fail(FU_E_ARG, "fu_qkv_rope_scatter: y_save needs 16-byte aligned rows");
     }
-    rc                 = set_smem(qkv_rope_scatter_kernel);
+    rc                 = set_smem(qkv_rope_scatter_kernel, SMEM_BYTES + QkvEpi::kExtraSmem);
     if (rc != FU_OK) {
         return rc;
     }
     const int grid = launch_grid(q->ctas, a.core.tiles_m * a.core.tiles_n);
-    qkv_rope_scatter_kernel<<<grid, THREADS, SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(a);
+    qkv_rope_scatter_kernel<<<grid, THREADS, SMEM_BYTES + QkvEpi::kExtraSmem, static_cast<cudaStream_t>(stream)>>>(a);
     FU_CUDA_OK(cudaGetLastError());
     return FU_OK;
 }

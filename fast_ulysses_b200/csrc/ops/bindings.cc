@@ -332,7 +332,7 @@ at::Tensor run_async(Group& g, const at::Tensor& input, int64_t mode, const Spli
     cuda_ok(cudaStreamWaitEvent(comm.stream(), ready, 0), "cudaStreamWaitEvent");
     cuda_ok(cudaEventDestroy(ready), "cudaEventDestroy");
     c10::cuda::CUDACachingAllocator::recordStream(p.x.storage().data_ptr(), comm);
-    run_prepared(g, p, comm.stream(), FU_A2A_MINOR_SHARE);
+    run_prepared(g, p, comm.stream(), FU_A2A_MINOR_SHARE | (g.async_copy_engine() ? FU_A2A_COPY_ENGINE : 0));
     return p.output;
 }
 
@@ -538,6 +538,9 @@ TORCH_LIBRARY(fast_ulysses_b200, m)
         .def("set_output_pool", [](const c10::intrusive_ptr<fu::Group>& g, bool on) { g->set_output_pool(on); })
         .def("output_pool", [](const c10::intrusive_ptr<fu::Group>& g) { return g->output_pool(); })
         .def("pool_hits", [](const c10::intrusive_ptr<fu::Group>& g) { return g->pool_hits(); })
+        .def("set_async_copy_engine",
+             [](const c10::intrusive_ptr<fu::Group>& g, bool on) { g->set_async_copy_engine(on); })
+        .def("async_copy_engine", [](const c10::intrusive_ptr<fu::Group>& g) { return g->async_copy_engine(); })
         .def("symm_alloc", &fu::Group::symm_alloc)
         .def("symm_ptrs", &fu::Group::symm_ptrs)
         .def("barrier",

@@ -86,6 +86,10 @@ public:
     bool          output_pool() const { return pool_enabled_; }
     void          set_output_pool(bool on) { pool_enabled_ = on; }
     int64_t       pool_hits() const { return pool_hits_; }
+    // Whether the asynchronous call moves its payload with the copy engines (FU_A2A_COPY_ENGINE)
+    // instead of the kernel. A local choice: both transports speak the same handshake.
+    bool          async_copy_engine() const { return async_copy_engine_; }
+    void          set_async_copy_engine(bool on) { async_copy_engine_ = on; }
     at::Tensor    make_output(at::IntArrayRef shape, at::ScalarType dtype, int64_t window_bytes);
     const Window* window_of(const at::Tensor& t) const;
     // A caller-owned symmetric byte buffer for the fused operators (q/k/v windows, attention
@@ -132,6 +136,7 @@ private:
     bool        alive_      = true;
     uint32_t    timeout_ms_ = 0;
     int         test_flags_ = 0;
+    bool        async_copy_engine_ = false;
     int         ctas_       = 0;
     int64_t     allocations_ = 0;
 

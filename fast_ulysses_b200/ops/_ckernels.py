@@ -18,6 +18,7 @@ FU_A2A_NO_HANDSHAKE = 1
 FU_A2A_STAMPS = 2
 FU_A2A_EARLY_PUBLISH = 4
 FU_A2A_LDST = 8
+FU_A2A_COPY_ENGINE = 128
 FU_A2A_MUTE = 16
 FU_A2A_MINOR_SHARE = 32
 FU_QKV_W_KN = 64

@@ -264,6 +264,21 @@ class UlyssesGroup:
         if self.device.type != "cpu":
             self._handle.set_output_pool(bool(enabled))
 
+    def set_async_transport(self, transport: str) -> None:
+        """How ``all_to_all_4d_async`` moves its payload from now on.
+
+        ``"kernel"`` (default): the same persistent kernel as the synchronous call, on a third of
+        the SMs. Fastest on its own, but a GEMM running beside it loses those SMs, and a
+        persistent GEMM with a fixed tile schedule finishes later by about the whole exchange.
+        ``"copy_engine"``: the routes go to the copy engines (one pitched copy per peer and batch)
+        between two one-warp handshake kernels, as in the reference (src/transfer.cu:68-126): no
+        SM is held while the payload moves, so compute beside the call keeps the device.
+        A local choice; ranks may differ (both transports speak the same handshake)."""
+        if transport not in ("kernel", "copy_engine"):
+            raise ValueError(f"transport must be 'kernel' or 'copy_engine', got {transport!r}")
+        if self.device.type != "cpu":
+            self._handle.set_async_copy_engine(transport == "copy_engine")
+
     def destroy(self) -> None:
         """Release the group's windows. Collective. Buffers from ``empty_output()`` are yours."""
         if self._destroyed:

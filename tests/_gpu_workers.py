@@ -480,6 +480,69 @@ def async_input_may_be_overwritten(rank, world):
     assert bad == 0, f"{bad} results saw the overwrite of x"
 
 
+def copy_engine_transport(rank, world):
+    """The asynchronous call on the copy engines against the kernel transport: bit-exact in both
+    modes, with even, uneven and empty shards, batches, out= and lent results; ranks that mix the
+    two transports; the synchronous call through the same data path; two phases per call."""
+    dev = torch.device("cuda", rank)
+    g = UlyssesGroup(device=dev)
+    torch.manual_seed(100 + rank)
+    heads = 2 * world
+    uneven_seq = [40 + 8 * p for p in range(world)]
+    uneven_seq[-1] = 0  # one empty shard
+    uneven_heads = [3] * world
+    uneven_heads[0] = 1
+    cases = [((1, 96, heads, 128), {}), ((2, 50, heads, 64), {}), ((3, 7, 4 * world, 32), {}),
+             ((2, uneven_seq[rank], sum(uneven_heads), 128), {"seq_splits": uneven_seq, "head_splits": uneven_heads})]
+    for setting in ("all", "mixed"):
+        mine = "copy_engine" if setting == "all" or rank % 2 == 0 else "kernel"
+        for shape, kw in cases:
+            x = torch.randn(shape, device=dev, dtype=torch.bfloat16)
+            g.set_async_transport("kernel")
+            want = g.all_to_all_4d_async(x, **kw).wait().clone()
+            back_want = g.all_to_all_4d_async(want, mode=1, **kw).wait().clone()
+            assert torch.equal(back_want, x), (shape, "round trip of the kernel transport")
+            g.set_async_transport(mine)
+            got = g.all_to_all_4d_async(x, **kw).wait()
+            assert torch.equal(got, want), (setting, shape, "mode 0")
+            back = g.all_to_all_4d_async(got, mode=1, **kw).wait()
+            assert torch.equal(back, x), (setting, shape, "mode 1")
+            out = g.empty_output(x, **kw)
+            g.all_to_all_4d_async(x, out=out, **kw).wait()
+            assert torch.equal(out, want), (setting, shape, "out= a symmetric buffer")
+            plain = torch.empty_like(want)
+            g.all_to_all_4d_async(x, out=plain, **kw).wait()
+            assert torch.equal(plain, want), (setting, shape, "out= an ordinary tensor")
+            lent = g.all_to_all_4d_async(x, lend=True, **kw).wait()
+            assert torch.equal(lent, want), (setting, shape, "lent window")
+            del lent
+    # many rounds with a rotating late rank: the handshakes around the copies must hold
+    g.set_async_transport("copy_engine")
+    x = torch.empty(1, 1024, heads, 128, device=dev, dtype=torch.bfloat16)
+    probe = torch.empty(1, 1024, heads, 128, device=dev, dtype=torch.bfloat16)
+    g.all_to_all_4d_async(x.zero_()).wait()
+    torch.cuda.synchronize()
+    e0 = g._handle.epoch_debug(probe, 1)
+    bad = 0
+    for i in range(40):
+        x.fill_(float(i + 1))
+        if rank == i % world:
+            torch.cuda._sleep(2_000_000)
+        bad += int(not bool(torch.all(g.all_to_all_4d_async(x).wait() == float(i + 1))))
+    torch.cuda.synchronize()
+    assert bad == 0, f"{bad} rounds delivered something else than that round's payload"
+    assert g._handle.epoch_debug(probe, 1) == e0 + 2 * 40, "two phases per call on the asynchronous window"
+    # the synchronous call through the same data path (the pool is a device-side choice, so off)
+    g.set_output_pool(False)
+    g._handle.set_test_flags(128)  # FU_A2A_COPY_ENGINE
+    x = torch.randn(2, 64, heads, 128, device=dev, dtype=torch.bfloat16)
+    y = g.all_to_all_4d(x)
+    g._handle.set_test_flags(0)
+    assert torch.equal(y, g.all_to_all_4d(x))
+    g.check()
+    g.destroy()
+
+
 def pooled_result_read_on_a_side_stream(rank, world):
     """A pooled result (the default return of all_to_all_4d) read on a side stream: record_stream()
     does nothing for it, the documented rule is to order the side stream before dropping the

@@ -83,14 +83,14 @@ def emulate(b, seq, heads, d, mode, dtype, flags, copy_out, ctas=0, own_direct=T
         assert status == 0, f"rank {r} status {status}"
 
 
-@pytest.mark.parametrize("flags", [0, ck.FU_A2A_LDST], ids=["bulk", "ldst"])
+@pytest.mark.parametrize("flags", [0, ck.FU_A2A_LDST, ck.FU_A2A_COPY_ENGINE], ids=["bulk", "ldst", "copy_engine"])
 @pytest.mark.parametrize("mode", [0, 1])
 @pytest.mark.parametrize("ws", [1, 2, 3, 4, 8])
 def test_even_shards(flags, mode, ws):
     emulate(2, [40] * ws, [2] * ws, 64, mode, torch.bfloat16, flags, copy_out=True)
 
 
-@pytest.mark.parametrize("flags", [0, ck.FU_A2A_LDST], ids=["bulk", "ldst"])
+@pytest.mark.parametrize("flags", [0, ck.FU_A2A_LDST, ck.FU_A2A_COPY_ENGINE], ids=["bulk", "ldst", "copy_engine"])
 @pytest.mark.parametrize("mode", [0, 1])
 def test_uneven_and_empty_shards(flags, mode):
     emulate(1, [300, 212], [4, 4], 128, mode, torch.float32, flags, copy_out=True)
@@ -105,7 +105,7 @@ def test_dtypes(dtype, d):
         emulate(2, [5, 9, 2], [3, 1, 2], d, mode, dtype, 0, copy_out=True)
 
 
-@pytest.mark.parametrize("flags", [0, ck.FU_A2A_LDST], ids=["bulk", "ldst"])
+@pytest.mark.parametrize("flags", [0, ck.FU_A2A_LDST, ck.FU_A2A_COPY_ENGINE], ids=["bulk", "ldst", "copy_engine"])
 def test_flat_copy_out_without_own_direct(flags):
     emulate(2, [17, 5, 33], [2, 3, 1], 64, 0, torch.bfloat16, flags, copy_out=True, own_direct=False)
     emulate(2, [17, 5, 33], [2, 3, 1], 64, 1, torch.bfloat16, flags, copy_out=True, own_direct=False)

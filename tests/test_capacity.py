@@ -58,6 +58,17 @@ def test_a2a_route_past_a_pool_buffer_is_refused():
     assert "pool buffers hold" in last_error()
 
 
+def test_a2a_copy_engine_transport_refuses_the_output_pool():
+    a = a2a_args()
+    a.flags = 128  # FU_A2A_COPY_ENGINE
+    assert ck.lib().fu_a2a4d_check(C.byref(a)) == 0, last_error()
+    a.n_pool, a.pool_bytes = 1, a.win_bytes
+    for p in range(2):
+        a.peer_pool[p][0] = BASE + (8 + p) * (1 << 30)
+    assert ck.lib().fu_a2a4d_check(C.byref(a)) != 0
+    assert "copy-engine transport" in last_error()
+
+
 def test_a2a_direct_own_share_past_the_output_is_refused():
     a = a2a_args()
     a.out, a.out_bytes, a.own_direct = BASE + (1 << 40), 8 * 256 * 2 - 256, 1

@@ -70,6 +70,11 @@ def test_async_input_may_be_overwritten(world):
     run_ranks(world, "_gpu_workers", "async_input_may_be_overwritten", backend="nccl", timeout=300)
 
 
+@pytest.mark.parametrize("world", world_sizes())
+def test_copy_engine_transport(world):
+    run_ranks(world, "_gpu_workers", "copy_engine_transport", backend="nccl", timeout=600)
+
+
 @pytest.mark.parametrize("world", world_sizes()[:1])
 def test_pooled_result_read_on_a_side_stream(world):
     run_ranks(world, "_gpu_workers", "pooled_result_read_on_a_side_stream", backend="nccl", timeout=300)
