@@ -119,46 +119,57 @@ def main():
             for _ in range(3):
                 a @ a
 
-        # `x` is never written here, so the asynchronous call reads it in place (stage=False)
-        def alone():
-            g.all_to_all_4d_async(x, stage=False).wait()
-
-        def serial():
-            gemms()
-            g.all_to_all_4d_async(x, stage=False).wait()
-
-        def concurrent():
-            h = g.all_to_all_4d_async(x, stage=False)
-            gemms()
-            h.wait()
-
-        # how long the GEMMs themselves take while the exchange runs beside them (events around the
-        # GEMMs only, on the caller's stream): an exchange can hide itself by taking SMs from them
-        def gemms_beside():
-            h = g.all_to_all_4d_async(x, stage=False)
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            gemms()
-            e1.record()
-            h.wait()
-            return e0, e1
+        # `x` is never written here, so the asynchronous call reads it in place (stage=False).
+        # Two forms of the call: "copying" returns a fresh tensor (window + copy-out), "lend"
+        # returns the window itself (nothing is copied out).
+        def exchange(form):
+            return g.all_to_all_4d_async(x, stage=False, lend=(form == "lend"))
 
         t_g = run(gemms, args.iters)
-        for transport in ("kernel", "copy_engine"):
+        want = g.all_to_all_4d(x).clone()
+        # (name, transport, test flags): the last row hands the copies that stay on the device to
+        # the driver's pitched copy as well (FU_A2A_CE_LOCAL_COPIES), for comparison
+        rows = [("kernel", "kernel", 0), ("copy_engine", "copy_engine", 0), ("copy_engine+driver_local_copies", "copy_engine", 512)]
+        for name, transport, test_flags in rows:
             g.set_async_transport(transport)
-            t_a = run(alone, args.iters)
-            t_s, t_c = run(serial, args.iters), run(concurrent, args.iters)
-            pairs = []
-            for _ in range(args.iters):
-                flush.zero_()
-                pairs.append(gemms_beside())
-            torch.cuda.synchronize()
-            beside = sorted(a.elapsed_time(b) for a, b in pairs)[len(pairs) // 2]
-            tb = torch.tensor([beside], device="cuda", dtype=torch.float64)
-            dist.all_reduce(tb, op=dist.ReduceOp.MAX)
-            emit(rank, mode="overlap", transport=transport, shape=args.shape, world=world, gemm_ms=t_g, a2a_ms=t_a,
-                 serial_ms=t_s, concurrent_ms=t_c, hidden_pct=100.0 * (t_s - t_c) / t_a,
-                 gemm_beside_exchange_ms=float(tb), gemm_slowdown_pct=100.0 * (float(tb) - t_g) / t_g)
+            g._handle.set_test_flags(test_flags)
+            for form in ("copying", "lend"):
+                assert torch.equal(exchange(form).wait(), want), (name, form)
+
+                def alone():
+                    exchange(form).wait()
+
+                def serial():
+                    gemms()
+                    exchange(form).wait()
+
+                def concurrent():
+                    h = exchange(form)
+                    gemms()
+                    h.wait()
+
+                t_a = run(alone, args.iters)
+                t_s, t_c = run(serial, args.iters), run(concurrent, args.iters)
+                # how long the GEMMs themselves take while the exchange runs beside them (events around
+                # the GEMMs only, on the caller's stream): an exchange can hide itself by taking SMs from them
+                pairs = []
+                for _ in range(args.iters):
+                    flush.zero_()
+                    h = exchange(form)
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record()
+                    gemms()
+                    e1.record()
+                    h.wait()
+                    pairs.append((e0, e1))
+                torch.cuda.synchronize()
+                beside = sorted(p0.elapsed_time(p1) for p0, p1 in pairs)[len(pairs) // 2]
+                tb = torch.tensor([beside], device="cuda", dtype=torch.float64)
+                dist.all_reduce(tb, op=dist.ReduceOp.MAX)
+                emit(rank, mode="overlap", transport=name, form=form, shape=args.shape, world=world, gemm_ms=t_g, a2a_ms=t_a,
+                     serial_ms=t_s, concurrent_ms=t_c, hidden_pct=100.0 * (t_s - t_c) / t_a,
+                     gemm_beside_exchange_ms=float(tb), gemm_slowdown_pct=100.0 * (float(tb) - t_g) / t_g)
+        g._handle.set_test_flags(0)
     elif args.mode == "fp8":
         from fast_ulysses_b200.ops import fp8
 

@@ -2,7 +2,7 @@
 L2 so that DRAM counters mean something, a few hundred MB on the device, one to three launches of
 the kernel of interest after a short warm-up.
 
-    python benchmarks/profile_cases.py a2a|gemm|qkv|outproj|fmha_fwd|fmha_bwd|fmha_bwd_det
+    python benchmarks/profile_cases.py a2a|gemm|gemm_pair|qkv|outproj|fmha_fwd|fmha_bwd|fmha_bwd_det
 
 Each case prints the CUDA-event time of its last launch, so the same command is also a quick
 timing check when run without a profiler.
@@ -53,6 +53,32 @@ def case_gemm():
     b = torch.randn(8192, 8192, device="cuda").bfloat16()
     ms = _time(lambda: gemm.gemm_bf16(a, b))
     print(f"gemm 8192^3: {ms:.4f} ms, {2 * 8192 ** 3 / ms / 1e9:.0f} TFLOP/s")
+
+
+def case_gemm_pair():
+    """The single-CTA kernel, the CTA-pair kernel and cuBLAS on 8192 cubed: median of 15 launches,
+    256 MiB L2 flush before each."""
+    from fast_ulysses_b200.ops import gemm
+
+    a = torch.randn(8192, 8192, device="cuda").bfloat16()
+    b = torch.randn(8192, 8192, device="cuda").bfloat16()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    for name, fn in (("single CTA", lambda: gemm.gemm_bf16(a, b, pair=False)),
+                     ("CTA pairs", lambda: gemm.gemm_bf16(a, b, pair=True)), ("cuBLAS", lambda: a @ b.t())):
+        for _ in range(5):
+            fn()
+        gemm.check_errors()
+        times = []
+        for _ in range(15):
+            flush.zero_()
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0.record()
+            fn()
+            t1.record()
+            torch.cuda.synchronize()
+            times.append(t0.elapsed_time(t1))
+        ms = sorted(times)[len(times) // 2]
+        print(f"gemm 8192^3, {name}: {ms:.4f} ms, {2 * 8192 ** 3 / ms / 1e9:.0f} TFLOP/s")
 
 
 def _fake_world(seq, head_splits, hidden):
@@ -144,7 +170,7 @@ def case_fmha_bwd_det():
     print(f"fmha bwd (two passes, no atomics) S=16384 H=5: {ms:.4f} ms, {10 * 16384 ** 2 * 128 * 5 / ms / 1e9:.0f} TFLOP/s")
 
 
-CASES = {"a2a": case_a2a, "gemm": case_gemm, "qkv": case_qkv, "outproj": case_outproj, "fmha_fwd": case_fmha_fwd,
+CASES = {"a2a": case_a2a, "gemm": case_gemm, "gemm_pair": case_gemm_pair, "qkv": case_qkv, "outproj": case_outproj, "fmha_fwd": case_fmha_fwd,
          "fmha_bwd": case_fmha_bwd, "fmha_bwd_det": case_fmha_bwd_det}
 
 if __name__ == "__main__":

@@ -421,7 +421,9 @@ __global__ void __launch_bounds__(kBulk ? 32 : kLdstThreads, kBulk ? 1 : kLdstCt
             own->stamps[4] = globaltimer_ns();
         }
         __threadfence();
-        *reinterpret_cast<volatile uint64_t*>(&own->epoch) = base + 2;
+        if (!(a.flags & FU_A2A_KEEP_EPOCH)) {
+            *reinterpret_cast<volatile uint64_t*>(&own->epoch) = base + 2;
+        }
     }
 }
 
@@ -747,6 +749,8 @@ int build_args(const FuA2AArgs* args, KArgs& k)
 
 }  // namespace
 
+extern "C" int fu_a2a4d(const FuA2AArgs* args, void* stream_v);
+
 namespace {
 
 // One route on the copy engines: a pitched copy per batch (a flat one where both sides are dense).
@@ -770,24 +774,72 @@ int copy_route(const FuRoute& r, const uint8_t* src_base, uint8_t* dst_base, cud
     return FU_OK;
 }
 
-// The whole call on the copy engines. `in` has passed build_args(), so every route lies inside the
-// buffers it names. The routes run one after another on the caller's stream: one copy-engine flow
-// fills a GPU's NVLink egress, so nothing is gained by spreading them over streams, and the order in
-// which `in.routes` lists the peers (next rank up first) keeps every rank's ingress fed by one sender
-// at a time.
+// The whole call with the copy engines as the data plane. `in` has passed build_args(), so every
+// route lies inside the buffers it names. The routes to peers run one after another on the
+// caller's stream: one copy-engine flow fills a GPU's NVLink egress, so nothing is gained by
+// spreading them over streams, and the order in which `in.routes` lists the peers (next rank up
+// first) keeps every rank's ingress fed by one sender at a time.
+// What stays on this device (the own share, and the copy-out of a copying call) is moved by a
+// small launch of the exchange kernel itself, with handshakes off: the driver serves a pitched
+// copy within one device with a kernel of its own choosing, not with a copy engine, so nothing
+// is saved by asking it. FU_A2A_CE_LOCAL_COPIES asks it all the same (for measurements).
+constexpr int kCeLocalCtas = 16;
+
 int launch_copy_engine(const FuA2AArgs& in, const KArgs& k, cudaStream_t stream)
 {
-    const bool handshake = !(in.flags & FU_A2A_NO_HANDSHAKE);
-    const bool copy_out  = in.out && in.out_bytes > 0;
+    const bool handshake    = !(in.flags & FU_A2A_NO_HANDSHAKE);
+    const bool copy_out     = in.out && in.out_bytes > 0;
+    const bool local_kernel = !(in.flags & FU_A2A_CE_LOCAL_COPIES);
+    // A launch of the exchange kernel that moves only local data and leaves the handshakes and the
+    // phase counter to the one-warp kernels around the copies.
+    auto helper = [&](bool own_share) -> int {
+        FuA2AArgs h = in;
+        h.flags     = (in.flags & (FU_A2A_LDST | FU_A2A_MINOR_SHARE)) | FU_A2A_NO_HANDSHAKE | FU_A2A_KEEP_EPOCH;
+        h.ctas      = in.ctas > 0 ? std::min(in.ctas, kCeLocalCtas) : kCeLocalCtas;
+        for (int p = 0; p < FU_MAX_WORLD; ++p) {
+            h.peer_slot[p] = 0;
+        }
+        if (own_share) {
+            h.n_routes = 0;
+            for (int i = 0; i < in.n_routes; ++i) {
+                if (in.routes[i].peer == in.rank) {
+                    h.routes[h.n_routes++] = in.routes[i];
+                }
+            }
+            h.n_out_routes = 0;
+            if (!(copy_out && in.own_direct)) {  // the own share goes to the own window: nothing else is written
+                h.out       = nullptr;
+                h.out_bytes = 0;
+            }
+            if (h.n_routes == 0) {
+                return FU_OK;
+            }
+        }
+        else {
+            h.n_routes = 0;  // only the copy-out runs
+        }
+        return fu_a2a4d(&h, stream);
+    };
+    if (local_kernel) {
+        // Touches the caller's tensor or the own window only, which no peer reads: it need not
+        // wait for anybody, so it goes first.
+        const int rc = helper(true);
+        if (rc != FU_OK) {
+            return rc;
+        }
+    }
     if (handshake) {
         ce_phase_kernel<<<1, 32, 0, stream>>>(k.peers, 1, in.flags);
         FU_CUDA_OK(cudaGetLastError());
     }
     for (int i = 0; i < in.n_routes; ++i) {
-        const FuRoute& r      = in.routes[i];
-        const bool     direct = copy_out && in.own_direct && r.peer == in.rank;
-        uint8_t*       dst    = direct ? static_cast<uint8_t*>(in.out) : static_cast<uint8_t*>(in.peer_win[r.peer]);
-        const int      rc     = copy_route(r, static_cast<const uint8_t*>(in.src), dst, stream);
+        const FuRoute& r = in.routes[i];
+        if (local_kernel && r.peer == in.rank) {
+            continue;
+        }
+        const bool direct = copy_out && in.own_direct && r.peer == in.rank;
+        uint8_t*   dst    = direct ? static_cast<uint8_t*>(in.out) : static_cast<uint8_t*>(in.peer_win[r.peer]);
+        const int  rc     = copy_route(r, static_cast<const uint8_t*>(in.src), dst, stream);
         if (rc != FU_OK) {
             return rc;
         }
@@ -797,8 +849,12 @@ int launch_copy_engine(const FuA2AArgs& in, const KArgs& k, cudaStream_t stream)
         FU_CUDA_OK(cudaGetLastError());
     }
     if (copy_out) {
+        const bool routed = in.n_out_routes > 0 || in.own_direct;
+        if (local_kernel && (!routed || in.n_out_routes > 0)) {
+            return helper(false);
+        }
         const uint8_t* win = static_cast<const uint8_t*>(in.peer_win[in.rank]);
-        if (in.n_out_routes > 0 || in.own_direct) {
+        if (routed) {
             for (int i = 0; i < in.n_out_routes; ++i) {
                 const int rc = copy_route(in.out_routes[i], win, static_cast<uint8_t*>(in.out), stream);
                 if (rc != FU_OK) {

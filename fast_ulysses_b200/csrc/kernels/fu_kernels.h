@@ -69,6 +69,11 @@ enum {
                                 // whole device. Same handshake protocol as the kernel transport, so
                                 // ranks may mix the two. Not available to a call that may use the
                                 // output pool (the host cannot know which buffer a peer chose).
+    FU_A2A_KEEP_EPOCH    = 256, // leave the window's phase counter alone (a helper launch inside a
+                                // call whose handshakes are run by other launches)
+    FU_A2A_CE_LOCAL_COPIES = 512, // with FU_A2A_COPY_ENGINE: the copies that stay on this device (own
+                                // share, copy-out) also go through cudaMemcpy2DAsync instead of a
+                                // small launch of the exchange kernel
 };
 
 // Output pool. A rank may ask its peers, per call, to write into one of up to FU_POOL_SLOTS extra
@@ -132,7 +137,12 @@ FU_API int fu_barrier(FuCtrl* const* peer_ctrl, int rank, int world, uint32_t ti
 // flags: an operand may be given with the contraction along its rows instead of its columns
 // (A stored k x m with pitch lda, B stored k x n with pitch ldb). The weight gradient of a linear
 // layer, dW = dY^T X, is then a GEMM over dY and X as they lie in memory.
-enum { FU_GEMM_A_KM = 1, FU_GEMM_B_KN = 2 };
+enum {
+    FU_GEMM_A_KM = 1,
+    FU_GEMM_B_KN = 2,
+    FU_GEMM_PAIR = 4,    // run on CTA pairs (256 x 256 tiles, tcgen05 cta_group::2) whatever the default is
+    FU_GEMM_SINGLE = 8,  // run on single CTAs (128 x 256 tiles) whatever the default is
+};
 typedef struct FuGemmArgs {
     const void*  a;
     const void*  b;
@@ -345,11 +355,12 @@ FU_API int fu_quant_e4m3_block128(const void* x_bf16, void* packed, int64_t bloc
 FU_API int fu_dequant_e4m3_block128(const void* packed, void* x_bf16, int64_t blocks, void* stream);
 
 // The all-to-all of a (b, s, n, 128) bf16 tensor with the payload carried as block-scaled e4m3, in
-// one launch: quantised in the store path into the peers' windows (packed rows of 144 bytes),
-// expanded into the bf16 result `out` after the closing handshake. `routes` are the routes of the
-// bf16 plan (byte quantities of 256-byte rows); the launcher rescales the destination side.
-// `win_bytes` is the size of every window in PACKED bytes, `out_rows` the (token, head) rows of
-// the result, `src_bytes` the extent of the input.
+// one launch: quantised in the store path into the peers' windows, expanded into the bf16 result
+// `out` after the closing handshake. `routes` are the routes of the bf16 plan (byte quantities of
+// 256-byte rows); the launcher rescales the destination side. `win_bytes` is the size of every
+// window, THE SAME ON EVERY RANK, at 144 bytes per (token, head) row it must hold (inside, 128-byte
+// payloads and 4-byte scales lie in two planes whose split follows from `win_bytes`); `out_rows`
+// the (token, head) rows of the result, `src_bytes` the extent of the input. 16-byte aligned operands.
 typedef struct FuA2AFp8Args {
     const void* src;
     void*       out;

@@ -15,6 +15,7 @@
 #include "tma_host.h"
 
 #include <algorithm>
+#include <cstdlib>
 
 namespace {
 
@@ -164,6 +165,12 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_plain_kernel(const __grid_con
 {
     PlainEpi epi = a.epi;
     run(a.core, epi);
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1) gemm_pair_kernel(const __grid_constant__ PlainArgs a)
+{
+    PlainEpi epi = a.epi;
+    run_pair(a.core, epi);
 }
 
 // ---- fused QKV epilogue: RMSNorm + 3D RoPE + scatter ---------------------------------------------------
@@ -513,17 +520,72 @@ int launch_grid(int ctas, int tiles)
     return std::max(1, std::min(g, tiles));
 }
 
+// Raises a kernel's dynamic shared-memory limit once per (device, kernel). Keyed by the kernel's
+// address: two kernels with the same signature share one instantiation of this template.
 template <class K>
 int set_smem(K kernel, int bytes = SMEM_BYTES)
 {
-    static bool done[64] = {};
-    int         dev      = 0;
+    struct Done {
+        int         dev;
+        const void* fn;
+    };
+    static Done done[256];
+    static int  n_done = 0;
+    int         dev    = 0;
     FU_CUDA_OK(cudaGetDevice(&dev));
-    if (dev < 64 && !done[dev]) {
-        FU_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
-        done[dev] = true;
+    const void* fn = reinterpret_cast<const void*>(kernel);
+    for (int i = 0; i < n_done; ++i) {
+        if (done[i].dev == dev && done[i].fn == fn) {
+            return FU_OK;
+        }
+    }
+    FU_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+    if (n_done < 256) {
+        done[n_done++] = Done{dev, fn};
     }
     return FU_OK;
+}
+
+// How many CTA pairs of the pair kernel the device holds at once (GPCs with an odd number of SMs
+// leave one SM without a partner). Asked once per device.
+int pair_capacity()
+{
+    static int cached[64] = {};
+    int        dev        = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev >= 64) {
+        return 0;
+    }
+    if (cached[dev] == 0) {
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim          = dim3(2, 1, 1);
+        cfg.blockDim         = dim3(THREADS, 1, 1);
+        cfg.dynamicSmemBytes = PAIR_SMEM_BYTES;
+        cudaLaunchAttribute attr{};
+        attr.id               = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = 2;
+        attr.val.clusterDim.y = 1;
+        attr.val.clusterDim.z = 1;
+        cfg.attrs             = &attr;
+        cfg.numAttrs          = 1;
+        int n                 = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, gemm_pair_kernel, &cfg) != cudaSuccess || n < 1) {
+            (void)cudaGetLastError();
+            // the kernel carries its cluster shape itself; ask again without naming it
+            cfg.attrs    = nullptr;
+            cfg.numAttrs = 0;
+            n            = 0;
+            if (cudaOccupancyMaxActiveClusters(&n, gemm_pair_kernel, &cfg) != cudaSuccess || n < 1) {
+                (void)cudaGetLastError();
+                // Pairs do not wait for one another, so a grid larger than what is resident at once
+                // is merely scheduled in turns: assume every SM finds a partner.
+                int sms = 0;
+                cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+                n = sms / 2;
+            }
+        }
+        cached[dev] = n > 0 ? n : -1;
+    }
+    return cached[dev] > 0 ? cached[dev] : 0;
 }
 
 int fill_core(Core& core, const void* a, const void* b, int64_t m, int64_t n, int64_t k, int64_t lda, int64_t ldb,
@@ -540,7 +602,9 @@ int fill_core(Core& core, const void* a, const void* b, int64_t m, int64_t n, in
     if (rc != FU_OK) {
         return rc;
     }
-    rc = core.b_mn ? make_map_2d(&core.map_b, b, 2, k, n, ldb, 64, 64) : make_map_2d(&core.map_b, b, 2, n, k, ldb, BN, BK);
+    // a CTA pair splits B's rows of a tile between its two CTAs
+    const int b_rows = (flags & FU_GEMM_PAIR) ? BN / 2 : BN;
+    rc = core.b_mn ? make_map_2d(&core.map_b, b, 2, k, n, ldb, 64, 64) : make_map_2d(&core.map_b, b, 2, n, k, ldb, b_rows, BK);
     if (rc != FU_OK) {
         return rc;
     }
@@ -564,8 +628,16 @@ extern "C" int fu_gemm_bf16(const FuGemmArgs* g, void* stream)
         || (g->residual && (reinterpret_cast<uintptr_t>(g->residual) & 15u))) {
         return fu::fail(FU_E_ARG, "fu_gemm_bf16: C (and the residual) need 16-byte aligned rows");
     }
+    // CTA pairs are chosen per call (FU_GEMM_PAIR / FU_GEMM_SINGLE) or, for calls that say nothing,
+    // by the environment variable FU_GEMM_PAIR (read once).
+    static const bool pair_default = [] {
+        const char* e = std::getenv("FU_GEMM_PAIR");
+        return e && e[0] == '1';
+    }();
+    const bool pair  = (g->flags & FU_GEMM_PAIR) || (pair_default && !(g->flags & FU_GEMM_SINGLE));
+    const int  flags = pair ? (g->flags | FU_GEMM_PAIR) : (g->flags & ~FU_GEMM_PAIR);
     PlainArgs a{};
-    int       rc = fill_core(a.core, g->a, g->b, g->m, g->n, g->k, g->lda, g->ldb, g->err, g->flags);
+    int       rc = fill_core(a.core, g->a, g->b, g->m, g->n, g->k, g->lda, g->ldb, g->err, flags);
     if (rc != FU_OK) {
         return rc;
     }
@@ -584,6 +656,22 @@ extern "C" int fu_gemm_bf16(const FuGemmArgs* g, void* stream)
     if ((g->aux || g->c_pre) && ((g->n % 8) || (reinterpret_cast<uintptr_t>(g->aux) & 15u)
                                  || (reinterpret_cast<uintptr_t>(g->c_pre) & 15u))) {
         return fu::fail(FU_E_ARG, "fu_gemm_bf16: aux / c_pre need n %% 8 == 0 and 16-byte aligned rows");
+    }
+    if (pair) {
+        rc = set_smem(gemm_pair_kernel, PAIR_SMEM_BYTES);
+        if (rc != FU_OK) {
+            return rc;
+        }
+        const int pairs = pair_capacity();
+        if (pairs < 1) {
+            return fu::fail(FU_E_CUDA, "fu_gemm_bf16: this device cannot hold a cluster of two CTAs of the pair kernel");
+        }
+        const int tiles = ((a.core.tiles_m + 1) / 2) * a.core.tiles_n;
+        int       want  = g->ctas > 0 ? std::max(1, g->ctas / 2) : pairs;
+        want            = std::max(1, std::min(std::min(want, pairs), tiles));
+        gemm_pair_kernel<<<2 * want, THREADS, PAIR_SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(a);
+        FU_CUDA_OK(cudaGetLastError());
+        return FU_OK;
     }
     rc             = set_smem(gemm_plain_kernel);
     if (rc != FU_OK) {

@@ -242,6 +242,193 @@ __device__ __forceinline__ void run(const Core& core, Epi& epi, Src src = Src{},
     }
 }
 
+// ---- the same GEMM on CTA pairs ---------------------------------------------------------------------
+// Two CTAs of a cluster share a 256 x 256 output tile: each loads its own 128 rows of A and its own
+// 128 rows of B per K-block (32 KiB per stage instead of 48, so six stages fit), the even CTA
+// issues tcgen05.mma.cta_group::2 (M = 256) over both CTAs' shared memory, and each CTA's 128
+// accumulator lanes hold its own rows of the tile. Per 256 x 256 of output the pair moves 64 KiB
+// per K-block from L2 into shared memory where two single CTAs move 96: operand delivery is what
+// bounds the single-CTA kernel. Operand loads are ordinary per-CTA TMA loads; what crosses between
+// the CTAs are completion signals only (the loads' byte counts land on the even CTA's mbarrier,
+// the MMA's completion is signalled to both CTAs, the odd CTA's epilogue frees the accumulator
+// with a remote arrival).
+constexpr int PAIR_STAGES      = 6;
+constexpr int PAIR_B_BYTES     = (BN / 2) * BK * 2;
+constexpr int PAIR_STAGE_BYTES = A_BYTES + PAIR_B_BYTES;
+constexpr int PAIR_SMEM_BYTES  = PAIR_STAGES * PAIR_STAGE_BYTES + 1024;
+constexpr int PAIR_BAND        = 8;  // 256-row tiles per rasterisation band
+
+__device__ __forceinline__ void pair_tile_coords(const Core& c, int tiles_m2, int t, int& mt2, int& nt)
+{
+    const int band_tiles = PAIR_BAND * c.tiles_n;
+    const int band       = t / band_tiles;
+    const int r          = t - band * band_tiles;
+    const int rows       = min(PAIR_BAND, tiles_m2 - band * PAIR_BAND);
+    nt                   = r / rows;
+    mt2                  = band * PAIR_BAND + (r - nt * rows);
+}
+
+// `core.map_b` must have been built with a box of BN / 2 rows. Launch with cluster dimension 2.
+template <class Epi>
+__device__ __forceinline__ void run_pair(const Core& core, Epi& epi)
+{
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ uint64_t       full[PAIR_STAGES], empty[PAIR_STAGES], tmem_full[2], tmem_empty[2];
+    __shared__ uint32_t       tmem_holder;
+
+    const uint32_t base = (ptx::smem_addr(smem_raw) + 1023u) & ~1023u;
+    uint8_t*       ring = smem_raw + (base - ptx::smem_addr(smem_raw));
+    const int      warp = threadIdx.x >> 5;
+    const int      lane = threadIdx.x & 31;
+    const uint32_t half = ptx::cluster_ctarank();  // 0: issues the MMAs; 1: the other half of the tile
+    const int      pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
+    const int      tiles_m2    = (core.tiles_m + 1) / 2;
+    const int      total_tiles = tiles_m2 * core.tiles_n;
+    const int      kblocks     = (core.K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < PAIR_STAGES; ++s) {
+            ptx::mbar_init(&full[s], 1);
+            ptx::mbar_init(&empty[s], 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            ptx::mbar_init(&tmem_full[a], 1);
+            ptx::mbar_init(&tmem_empty[a], 8);  // four epilogue warps in each CTA
+        }
+        ptx::mbar_fence_init();
+        ptx::tma_prefetch_desc(&core.map_a);
+        ptx::tma_prefetch_desc(&core.map_b);
+    }
+    ptx::cluster_sync();  // both CTAs' barriers exist before either signals the other's
+    if (warp == 1) {
+        ptx::tmem_alloc_pair<TMEM_COLS>(&tmem_holder);
+        ptx::tmem_relinquish_pair();
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = tmem_holder;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool     ok = true;
+            for (int t = pair; t < total_tiles && ok; t += npairs) {
+                int mt2, nt;
+                pair_tile_coords(core, tiles_m2, t, mt2, nt);
+                const int m0 = (mt2 * 2 + static_cast<int>(half)) * BM;
+                const int n0 = nt * BN + static_cast<int>(half) * (BN / 2);
+                for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                    const int      s      = it % PAIR_STAGES;
+                    const uint32_t parity = ((it / PAIR_STAGES) & 1u) ^ 1u;
+                    if (!ptx::mbar_wait(&empty[s], parity)) {
+                        flag_error(core, ERR_PRODUCER_WAIT);
+                        ok = false;
+                        break;
+                    }
+                    uint8_t* sa = ring + s * PAIR_STAGE_BYTES;
+                    uint8_t* sb = sa + A_BYTES;
+                    if (half == 0) {
+                        ptx::mbar_expect_tx(&full[s], 2 * PAIR_STAGE_BYTES);  // both CTAs' bytes
+                    }
+                    if (!core.a_mn) {
+                        ptx::tma_load_2d_pair(sa, &core.map_a, kb * BK, m0, &full[s]);
+                    }
+                    else {
+                        for (int j = 0; j < BM / 64; ++j) {
+                            ptx::tma_load_2d_pair(sa + j * 8192, &core.map_a, m0 + j * 64, kb * BK, &full[s]);
+                        }
+                    }
+                    if (!core.b_mn) {
+                        ptx::tma_load_2d_pair(sb, &core.map_b, kb * BK, n0, &full[s]);
+                    }
+                    else {
+                        for (int j = 0; j < BN / 128; ++j) {
+                            ptx::tma_load_2d_pair(sb + j * 8192, &core.map_b, n0 + j * 64, kb * BK, &full[s]);
+                        }
+                    }
+                }
+            }
+        }
+        __syncwarp();
+    }
+    else if (warp == 1) {
+        if (lane == 0 && half == 0) {
+            const uint32_t idesc = ptx::make_idesc(1, 1, 2 * BM, BN, core.a_mn ? 1 : 0, core.b_mn ? 1 : 0);
+            const uint32_t a_lbo = core.a_mn ? 8192u : 16u, a_step = core.a_mn ? 128u : 2u;
+            const uint32_t b_lbo = core.b_mn ? 8192u : 16u, b_step = core.b_mn ? 128u : 2u;
+            uint32_t       it    = 0;
+            uint32_t       tcount = 0;
+            bool           ok    = true;
+            for (int t = pair; t < total_tiles && ok; t += npairs, ++tcount) {
+                const uint32_t acc = tcount & 1u;
+                if (!ptx::mbar_wait_cluster(&tmem_empty[acc], ((tcount >> 1) & 1u) ^ 1u)) {
+                    flag_error(core, ERR_MMA_WAIT_TMEM);
+                    ok = false;
+                    break;
+                }
+                ptx::tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * BN;
+                for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                    const int s = it % PAIR_STAGES;
+                    if (!ptx::mbar_wait(&full[s], (it / PAIR_STAGES) & 1u)) {
+                        flag_error(core, ERR_MMA_WAIT_FULL);
+                        ok = false;
+                        break;
+                    }
+                    ptx::tc_fence_after();
+                    const uint32_t sa     = base + s * PAIR_STAGE_BYTES;
+                    const uint64_t a_desc = ptx::smem_desc_sw128(sa, a_lbo, 1024);
+                    const uint64_t b_desc = ptx::smem_desc_sw128(sa + A_BYTES, b_lbo, 1024);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        ptx::mma_f16_ss_pair(d_tmem, a_desc + a_step * k, b_desc + b_step * k, idesc, (kb | k) != 0);
+                    }
+                    ptx::mma_commit_pair(&empty[s]);
+                }
+                if (ok) {
+                    ptx::mma_commit_pair(&tmem_full[acc]);
+                }
+            }
+        }
+        __syncwarp();
+    }
+    else {
+        const int epi_warp = warp - 2;
+        const int quarter  = warp & 3;
+        epi.open(epi_warp);
+        uint32_t tcount = 0;
+        bool     ok     = true;
+        for (int t = pair; t < total_tiles && ok; t += npairs, ++tcount) {
+            const uint32_t acc = tcount & 1u;
+            if (!ptx::mbar_wait(&tmem_full[acc], (tcount >> 1) & 1u)) {
+                flag_error(core, ERR_EPI_WAIT);
+                ok = false;
+                break;
+            }
+            ptx::tc_fence_after();
+            int mt2, nt;
+            pair_tile_coords(core, tiles_m2, t, mt2, nt);
+            epi.tile(tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16), mt2 * 2 + static_cast<int>(half), nt,
+                     quarter, lane);
+            ptx::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                ptx::mbar_arrive_cluster(ptx::cluster_addr(&tmem_empty[acc], 0));
+            }
+        }
+        epi.close(threadIdx.x - 64);
+    }
+
+    // Neither CTA may free its tensor memory, or leave, while the other can still signal it or
+    // read its shared memory.
+    ptx::tc_fence_before();
+    ptx::cluster_sync();
+    if (warp == 1) {
+        ptx::tmem_dealloc_pair<TMEM_COLS>(tmem_base);
+    }
+}
+
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi)
 {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);

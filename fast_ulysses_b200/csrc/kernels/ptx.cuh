@@ -270,6 +270,98 @@ __device__ __forceinline__ void mma_commit(uint64_t* bar)
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_addr(bar))
                  : "memory");
 }
+// ---- CTA pairs (cta_group::2): two CTAs of a cluster run one MMA over both SMs ---------------------
+// The even CTA of the pair issues; each CTA holds its own rows of A, its own half of B's rows and
+// its own 128 lanes of the accumulator. Operand tiles are fetched by ordinary per-CTA TMA loads
+// (nothing is multicast); only completion signals cross between the two CTAs.
+__device__ __forceinline__ uint32_t cluster_ctarank()
+{
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync()
+{
+    asm volatile("barrier.cluster.arrive.release;\n\tbarrier.cluster.wait.acquire;" ::: "memory");
+}
+// The address of this CTA's shared-memory object `p` as CTA `rank` of the cluster holds it.
+__device__ __forceinline__ uint32_t cluster_addr(const void* p, uint32_t rank)
+{
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr(p)), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_address)
+{
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_address) : "memory");
+}
+// Bounded wait that also orders what the OTHER CTA of the pair did before its arrival.
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, uint64_t limit_ns = 2000000000ull)
+{
+    const uint64_t t0 = globaltimer_ns();
+    for (uint32_t i = 0;; ++i) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(smem_addr(bar)), "r"(parity)
+            : "memory");
+        if (ok) {
+            return true;
+        }
+        if ((i & 255u) == 255u && (globaltimer_ns() - t0 > limit_ns || i > 0x7fffff00u)) {
+            return false;
+        }
+    }
+}
+// A tile of this CTA's operand share; the bytes are counted on the EVEN CTA's mbarrier (same offset).
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const void* map, int x, int y, uint64_t* bar)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], "
+        "[%2];" ::"r"(smem_addr(smem_dst)),
+        "l"(map), "r"(smem_addr(bar) & 0xFEFFFFFFu), "r"(x), "r"(y)
+        : "memory");
+}
+template <int NCOLS>
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_holder)
+{
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(smem_holder)),
+                 "n"(NCOLS)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair()
+{
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+template <int NCOLS>
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr)
+{
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "n"(NCOLS) : "memory");
+}
+__device__ __forceinline__ void mma_f16_ss_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// One arrival on the mbarrier at this offset in BOTH CTAs of the pair once every MMA issued so far
+// has completed (a completion signal sent to two CTAs; no data is multicast).
+__device__ __forceinline__ void mma_commit_pair(uint64_t* bar)
+{
+    asm volatile(
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+            smem_addr(bar)),
+        "h"(static_cast<uint16_t>(3))
+        : "memory");
+}
+
 __device__ __forceinline__ void tmem_ld_wait()
 {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");

@@ -7,9 +7,9 @@
 //
 // fu_a2a4d_fp8 is the exchange itself in that format, in ONE launch and with no pass of its own over
 // HBM for the quantisation: every rank reads its bf16 input once, quantises each (token, head) row in
-// registers and stores the packed row straight into the owning peer's window (0.56 of the bf16
-// bytes cross NVLink); after the closing handshake each rank expands its window into the bf16
-// result. The stand-alone kernels remain for callers that want the packed tensor itself.
+// registers and stores payload and scale straight into the owning peer's window (0.52 of the bf16
+// bytes cross NVLink; inside the windows payloads and scales lie in two planes, see below); after
+// the closing handshake each rank expands its window into the bf16 result. The stand-alone kernels remain for callers that want the packed tensor itself.
 //
 // The reference moves fp8/int8 tensors as opaque bytes (src/group.cc:54-62) and has no scaling.
 #include "fu_kernels.h"
@@ -81,52 +81,64 @@ __global__ void __launch_bounds__(256) dequant_e4m3_kernel(const uint8_t* packed
 }
 
 // ---- the exchange with quantisation in the store path ---------------------------------------------------
+// Inside the windows of this kernel the payloads and the scales lie in two planes: row i of a window
+// (rows in the order of the result: batch, token, local head) has its 128 e4m3 bytes at i * 128 and
+// its fp32 scale at win_rows * 128 + i * 4, with win_rows = win_bytes / 144 on every rank. A warp
+// quantises four neighbouring heads of a token at a time, so what it stores into a peer's window
+// is 512 contiguous, aligned payload bytes and 16 contiguous scale bytes: NVLink carries whole
+// 128-byte lines at its full rate and odd-sized pieces (a 144-byte row) at a fraction of it.
 struct Fp8Route {
     const uint8_t* src;  // bf16 rows of 256 bytes
-    uint8_t*       dst;  // packed rows of 144 bytes, in the peer's window
-    int64_t        src_pitch, src_batch, dst_pitch, dst_batch;  // bytes, per side
-    int64_t        rows, batches, heads_per_row, count;         // count = batches * rows * heads_per_row
+    uint8_t*       dst;  // the peer's window
+    int64_t        src_pitch, src_batch;              // bytes
+    int64_t        dst_row0, dst_pitch, dst_batch;    // window rows
+    int64_t        rows, batches, heads_per_row, groups, count;  // groups of 4 heads; count = batches * rows * groups
 };
 
 struct Fp8Args {
     Fp8Route       r[FU_MAX_WORLD];
     int            n;
     fu::Peers      peers;
-    const uint8_t* window;  // own window: packed rows in the layout of the result
+    const uint8_t* window;  // own window
     __nv_bfloat16* out;
     int64_t        out_rows;  // (token, head) rows of the result
+    int64_t        scale_off; // byte offset of the scale plane in every window
     int            handshake;
 };
 
-__device__ __forceinline__ void quant_row_store(uint2 raw, uint8_t* row, int lane)
+constexpr int kFp8Unroll = 2;  // groups of four rows whose loads are in flight per warp
+
+__device__ __forceinline__ uint32_t quant4(float a, float b, float c, float d, float inv)
 {
-    const float2 a    = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
-    const float2 b    = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
-    float        amax = fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(b.x), fabsf(b.y)));
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) {
-        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
-    }
-    const float scale = amax > 0.0f ? amax / 448.0f : 1.0f;
-    const float inv   = 1.0f / scale;
-    uint32_t    q     = 0;
-    q |= static_cast<uint32_t>(__nv_cvt_float_to_fp8(a.x * inv, __NV_SATFINITE, __NV_E4M3));
-    q |= static_cast<uint32_t>(__nv_cvt_float_to_fp8(a.y * inv, __NV_SATFINITE, __NV_E4M3)) << 8;
-    q |= static_cast<uint32_t>(__nv_cvt_float_to_fp8(b.x * inv, __NV_SATFINITE, __NV_E4M3)) << 16;
-    q |= static_cast<uint32_t>(__nv_cvt_float_to_fp8(b.y * inv, __NV_SATFINITE, __NV_E4M3)) << 24;
-    *reinterpret_cast<uint32_t*>(row + lane * 4) = q;
-    if (lane < 4) {
-        *reinterpret_cast<float*>(row + kBlock + lane * 4) = lane == 0 ? scale : 0.0f;
-    }
+    uint32_t q = 0;
+    q |= static_cast<uint32_t>(__nv_cvt_float_to_fp8(a * inv, __NV_SATFINITE, __NV_E4M3));
+    q |= static_cast<uint32_t>(__nv_cvt_float_to_fp8(b * inv, __NV_SATFINITE, __NV_E4M3)) << 8;
+    q |= static_cast<uint32_t>(__nv_cvt_float_to_fp8(c * inv, __NV_SATFINITE, __NV_E4M3)) << 16;
+    q |= static_cast<uint32_t>(__nv_cvt_float_to_fp8(d * inv, __NV_SATFINITE, __NV_E4M3)) << 24;
+    return q;
 }
 
-constexpr int kFp8Unroll = 4;  // rows whose loads are in flight per warp
+__device__ __forceinline__ void dequant4(uint32_t q, float scale, uint32_t& lo, uint32_t& hi)
+{
+    float v[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const __half_raw h = __nv_cvt_fp8_to_halfraw(static_cast<__nv_fp8_storage_t>((q >> (8 * k)) & 0xff), __NV_E4M3);
+        v[k]               = __half2float(*reinterpret_cast<const __half*>(&h)) * scale;
+    }
+    const __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]);
+    const __nv_bfloat162 b = __floats2bfloat162_rn(v[2], v[3]);
+    lo = *reinterpret_cast<const uint32_t*>(&a);
+    hi = *reinterpret_cast<const uint32_t*>(&b);
+}
 
 __global__ void __launch_bounds__(256) a2a4d_fp8_kernel(const __grid_constant__ Fp8Args a)
 {
     __shared__ uint32_t ticket;
     const int      lane   = threadIdx.x & 31;
     const int      warp   = threadIdx.x >> 5;
+    const int      sub    = lane >> 3;  // which of the warp's four rows this lane works on
+    const int      part   = lane & 7;   // which 16 values of that row
     const int64_t  warp0  = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
     const int64_t  nwarps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
     FuCtrl*        own    = a.peers.own;
@@ -144,23 +156,57 @@ __global__ void __launch_bounds__(256) a2a4d_fp8_kernel(const __grid_constant__ 
     for (int ri = 0; ri < a.n; ++ri) {
         const Fp8Route& r = a.r[ri];
         for (int64_t i0 = warp0 * kFp8Unroll; i0 < r.count; i0 += nwarps * kFp8Unroll) {
-            uint2    raw[kFp8Unroll];
-            uint8_t* to[kFp8Unroll];
+            uint4   raw[kFp8Unroll][2];
+            int64_t to[kFp8Unroll];  // window row this lane's values belong to, or -1
 #pragma unroll
             for (int u = 0; u < kFp8Unroll; ++u) {
                 const int64_t i = i0 + u;
+                to[u]           = -1;
                 if (i < r.count) {
-                    const int64_t h     = i % r.heads_per_row;
-                    const int64_t row   = (i / r.heads_per_row) % r.rows;
-                    const int64_t batch = i / (r.heads_per_row * r.rows);
-                    raw[u] = *reinterpret_cast<const uint2*>(r.src + batch * r.src_batch + row * r.src_pitch + h * 256 + lane * 8);
-                    to[u]  = r.dst + batch * r.dst_batch + row * r.dst_pitch + h * kPacked;
+                    const int64_t g     = i % r.groups;
+                    const int64_t row   = (i / r.groups) % r.rows;
+                    const int64_t batch = i / (r.groups * r.rows);
+                    const int64_t h     = g * 4 + sub;
+                    if (h < r.heads_per_row) {
+                        const uint4* from = reinterpret_cast<const uint4*>(r.src + batch * r.src_batch + row * r.src_pitch
+                                                                           + h * 256 + part * 32);
+                        raw[u][0] = from[0];
+                        raw[u][1] = from[1];
+                        to[u]     = r.dst_row0 + batch * r.dst_batch + row * r.dst_pitch + h;
+                    }
                 }
             }
 #pragma unroll
             for (int u = 0; u < kFp8Unroll; ++u) {
-                if (i0 + u < r.count) {
-                    quant_row_store(raw[u], to[u], lane);
+                float v[16];
+#pragma unroll
+                for (int k = 0; k < 2; ++k) {
+                    const uint32_t w[4] = {raw[u][k].x, raw[u][k].y, raw[u][k].z, raw[u][k].w};
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const float2 f   = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[j]));
+                        v[k * 8 + 2 * j]     = to[u] >= 0 ? f.x : 0.0f;
+                        v[k * 8 + 2 * j + 1] = to[u] >= 0 ? f.y : 0.0f;
+                    }
+                }
+                float amax = 0.0f;
+#pragma unroll
+                for (int k = 0; k < 16; ++k) {
+                    amax = fmaxf(amax, fabsf(v[k]));
+                }
+#pragma unroll
+                for (int off = 4; off > 0; off >>= 1) {  // the eight lanes of one row
+                    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+                }
+                const float scale = amax > 0.0f ? amax / 448.0f : 1.0f;
+                const float inv   = 1.0f / scale;
+                if (to[u] >= 0) {
+                    const uint4 q = make_uint4(quant4(v[0], v[1], v[2], v[3], inv), quant4(v[4], v[5], v[6], v[7], inv),
+                                               quant4(v[8], v[9], v[10], v[11], inv), quant4(v[12], v[13], v[14], v[15], inv));
+                    *reinterpret_cast<uint4*>(r.dst + to[u] * kBlock + part * 16) = q;
+                    if (part == 0) {
+                        *reinterpret_cast<float*>(r.dst + a.scale_off + to[u] * 4) = scale;
+                    }
                 }
             }
         }
@@ -181,33 +227,35 @@ __global__ void __launch_bounds__(256) a2a4d_fp8_kernel(const __grid_constant__ 
         fu::hs_await(a.peers, base + 2, FU_ST_CLOSE_TIMEOUT);
     }
     __syncthreads();
-    // Expand the own window (what the peers and this rank itself have written) into the result.
-    for (int64_t i0 = warp0 * kFp8Unroll; i0 < a.out_rows; i0 += nwarps * kFp8Unroll) {
-        uint32_t q[kFp8Unroll];
-        float    sc[kFp8Unroll];
+    // Expand the own window (what the peers and this rank itself have written) into the result:
+    // four rows per warp, 512 bytes of payload in, 1 KiB of bf16 out.
+    const int64_t out_groups = (a.out_rows + 3) / 4;
+    for (int64_t i0 = warp0 * kFp8Unroll; i0 < out_groups; i0 += nwarps * kFp8Unroll) {
+        uint4 q[kFp8Unroll];
+        float sc[kFp8Unroll];
 #pragma unroll
         for (int u = 0; u < kFp8Unroll; ++u) {
-            if (i0 + u < a.out_rows) {
-                const uint8_t* row = a.window + (i0 + u) * kPacked;
-                asm volatile("ld.global.u32 %0, [%1];" : "=r"(q[u]) : "l"(row + lane * 4));
-                asm volatile("ld.global.f32 %0, [%1];" : "=f"(sc[u]) : "l"(row + kBlock));
+            const int64_t row = (i0 + u) * 4 + sub;
+            if (row < a.out_rows) {
+                const uint8_t* from = a.window + row * kBlock + part * 16;
+                asm volatile("ld.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                             : "=r"(q[u].x), "=r"(q[u].y), "=r"(q[u].z), "=r"(q[u].w)
+                             : "l"(from));
+                asm volatile("ld.global.f32 %0, [%1];" : "=f"(sc[u]) : "l"(a.window + a.scale_off + row * 4));
             }
         }
 #pragma unroll
         for (int u = 0; u < kFp8Unroll; ++u) {
-            if (i0 + u < a.out_rows) {
-                float v[4];
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    const __half_raw h = __nv_cvt_fp8_to_halfraw(static_cast<__nv_fp8_storage_t>((q[u] >> (8 * k)) & 0xff), __NV_E4M3);
-                    v[k]               = __half2float(*reinterpret_cast<const __half*>(&h)) * sc[u];
-                }
-                const __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]);
-                const __nv_bfloat162 hi = __floats2bfloat162_rn(v[2], v[3]);
-                uint2                o;
-                o.x = *reinterpret_cast<const uint32_t*>(&lo);
-                o.y = *reinterpret_cast<const uint32_t*>(&hi);
-                *reinterpret_cast<uint2*>(a.out + (i0 + u) * kBlock + lane * 4) = o;
+            const int64_t row = (i0 + u) * 4 + sub;
+            if (row < a.out_rows) {
+                uint4 lo, hi;
+                dequant4(q[u].x, sc[u], lo.x, lo.y);
+                dequant4(q[u].y, sc[u], lo.z, lo.w);
+                dequant4(q[u].z, sc[u], hi.x, hi.y);
+                dequant4(q[u].w, sc[u], hi.z, hi.w);
+                uint4* to = reinterpret_cast<uint4*>(a.out + row * kBlock + part * 16);
+                to[0]     = lo;
+                to[1]     = hi;
             }
         }
     }
@@ -275,7 +323,7 @@ extern "C" int fu_a2a4d_fp8_check(const FuA2AFp8Args* a)
         || a->n_routes > FU_MAX_WORLD) {
         return fu::fail(FU_E_ARG, "fu_a2a4d_fp8: rank %d / world %d / %d routes", a->rank, a->world, a->n_routes);
     }
-    if ((reinterpret_cast<uintptr_t>(a->src) & 7u) || (reinterpret_cast<uintptr_t>(a->out) & 7u) || a->out_rows < 0
+    if ((reinterpret_cast<uintptr_t>(a->src) & 15u) || (reinterpret_cast<uintptr_t>(a->out) & 15u) || a->out_rows < 0
         || a->out_rows * kPacked > a->win_bytes) {
         return fu::fail(FU_E_ARG, "fu_a2a4d_fp8: unaligned operand, or %lld result rows in a window of %lld bytes",
                         (long long)a->out_rows, (long long)a->win_bytes);
@@ -325,16 +373,19 @@ extern "C" int fu_a2a4d_fp8(const FuA2AFp8Args* a, void* stream)
         }
         Fp8Route& o     = k.r[k.n++];
         o.src           = static_cast<const uint8_t*>(a->src) + r.src_off;
-        o.dst           = static_cast<uint8_t*>(a->peer_win[r.peer]) + r.dst_off / 256 * kPacked;
+        o.dst           = static_cast<uint8_t*>(a->peer_win[r.peer]);
         o.src_pitch     = r.src_pitch;
         o.src_batch     = r.src_batch;
-        o.dst_pitch     = r.dst_pitch / 256 * kPacked;
-        o.dst_batch     = r.dst_batch / 256 * kPacked;
+        o.dst_row0      = r.dst_off / 256;
+        o.dst_pitch     = r.dst_pitch / 256;
+        o.dst_batch     = r.dst_batch / 256;
         o.rows          = r.rows;
         o.batches       = r.batches;
         o.heads_per_row = r.row_bytes / 256;
-        o.count         = o.batches * o.rows * o.heads_per_row;
+        o.groups        = (o.heads_per_row + 3) / 4;
+        o.count         = o.batches * o.rows * o.groups;
     }
+    k.scale_off = a->win_bytes / kPacked * kBlock;  // the same on every rank: windows have one size
     for (int p = 0; p < a->world; ++p) {
         k.peers.ctrl[p] = a->peer_ctrl[p];
     }

@@ -49,7 +49,7 @@ def _tma_ready(x: torch.Tensor) -> torch.Tensor:
 def gemm_bf16(a: torch.Tensor, b: torch.Tensor, *, bias: torch.Tensor | None = None,
               residual: torch.Tensor | None = None, act: int = 0, out: torch.Tensor | None = None,
               ctas: int = 0, a_km: bool = False, b_kn: bool = False, aux: torch.Tensor | None = None,
-              store_pre: torch.Tensor | None = None) -> torch.Tensor:
+              store_pre: torch.Tensor | None = None, pair: bool | None = None) -> torch.Tensor:
     """``out[m, n] = act(a[m, :] . b[n, :] + bias[n]) + residual[m, n]`` (bf16 in, bf16 out).
 
     ``act``: 0 none, 1 GELU (tanh form), 2 GELU (erf form), 3 multiply by the derivative of the
@@ -58,7 +58,10 @@ def gemm_bf16(a: torch.Tensor, b: torch.Tensor, *, bias: torch.Tensor | None = N
 
     ``a_km`` / ``b_kn``: that operand is given with the contraction along its rows, ``a`` as
     ``(k, m)`` and ``b`` as ``(k, n)``; the kernel reads it as it lies in memory (no transposed
-    copy), which is what the weight gradient ``dY^T X`` of a linear layer wants."""
+    copy), which is what the weight gradient ``dY^T X`` of a linear layer wants.
+
+    ``pair``: run on pairs of CTAs (256 x 256 tiles, one tcgen05 MMA over two SMs) or on single
+    CTAs (128 x 256); ``None`` leaves the choice to the library's default."""
     assert a.is_cuda and b.is_cuda and a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
     assert a.dim() == 2 and b.dim() == 2
     a, b = _tma_ready(a), _tma_ready(b)
@@ -87,7 +90,7 @@ def gemm_bf16(a: torch.Tensor, b: torch.Tensor, *, bias: torch.Tensor | None = N
     if store_pre is not None:
         g.c_pre = store_pre.data_ptr()
     g.ctas = ctas
-    g.flags = (1 if a_km else 0) | (2 if b_kn else 0)
+    g.flags = (1 if a_km else 0) | (2 if b_kn else 0) | (0 if pair is None else 4 if pair else 8)
     g.err = error_word(a.device).data_ptr()
     lib = ck.lib()
     ck.check(lib.fu_gemm_bf16(C.byref(g), ck.stream_ptr()))

@@ -26,6 +26,35 @@ def test_gemm_matches_fp32(m, n, k):
     assert torch.allclose(got.float(), want, atol=0.5, rtol=2e-2)
 
 
+@pytest.mark.parametrize("m,n,k", [(256, 256, 64), (128, 256, 256), (300, 520, 200), (1000, 384, 320), (77, 40, 72),
+                                   (2048, 1536, 1024), (4096, 2048, 2048)])
+def test_cta_pair_kernel_matches_fp32_and_the_single_cta_kernel_bit_for_bit(m, n, k):
+    """256 x 256 tiles on pairs of CTAs (tcgen05 cta_group::2): the same products summed in the same
+    order as the 128 x 256 single-CTA kernel, so not a bit may differ."""
+    torch.manual_seed(m + n + k)
+    a = torch.randn(m, k, device="cuda").bfloat16()
+    b = torch.randn(n, k, device="cuda").bfloat16()
+    bias = torch.randn(n, device="cuda")
+    got = gemm.gemm_bf16(a, b, bias=bias, act=1, pair=True)
+    single = gemm.gemm_bf16(a, b, bias=bias, act=1, pair=False)
+    gemm.check_errors()
+    want = torch.nn.functional.gelu(a.float() @ b.float().t() + bias, approximate="tanh")
+    assert rel_err(got, want) < 5e-3
+    assert torch.equal(got, single)
+
+
+@pytest.mark.parametrize("a_km,b_kn", [(True, True), (False, True), (True, False)])
+def test_cta_pair_kernel_with_the_contraction_along_rows(a_km, b_kn):
+    torch.manual_seed(11)
+    m, n, k = 5120, 384, 9450
+    a = (torch.randn(m, k, device="cuda") * 0.5).bfloat16()
+    b = (torch.randn(n, k, device="cuda") * 0.5).bfloat16()
+    got = gemm.gemm_bf16(a.t().contiguous() if a_km else a, b.t().contiguous() if b_kn else b, a_km=a_km, b_kn=b_kn,
+                         pair=True)
+    gemm.check_errors()
+    assert rel_err(got, a.float() @ b.float().t()) < 5e-3
+
+
 @pytest.mark.parametrize("act", [0, 1, 2])
 def test_fused_epilogue(act):
     torch.manual_seed(act)
