@@ -9,7 +9,7 @@ over ranks) and the fraction of its roofline, defined as the slower of
     burst figure: the kernel is timed in isolation), and
   * the bytes that must cross NVLink at the measured peer-copy rate: `--link-gbs`, which should be
     the per-flow figure that `benchmarks/bench_a2a.py --mode link` printed on the same machine
-    (default 770, an earlier measurement on this pool), and
+    (default 636, what that mode measured for one flow through the bulk path at 4 and 8 GPUs of this pool), and
   * for the memory-bound gradient pull, its local HBM bytes at the measured copy rate (`hbm_gbs`).
 Rank 0 prints one JSON line per kernel. Nothing here runs under a profiler.
 """
@@ -46,7 +46,7 @@ def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--tokens", type=int, default=75600)
     ap.add_argument("--iters", type=int, default=15)
-    ap.add_argument("--link-gbs", type=float, default=770.0)
+    ap.add_argument("--link-gbs", type=float, default=636.0)
     args = ap.parse_args()
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
