@@ -57,6 +57,8 @@ def main() -> int:
             w(f"bench_a2a --mode {mode} ({args.gpus} GPUs)", "\n".join(l for l in out.splitlines() if l.startswith("{")))
             if "{" not in out:
                 failed.append(mode)
+        out = sh(run + ["benchmarks/bench_fused.py"])
+        w(f"bench_fused ({args.gpus} GPUs)", "\n".join(l for l in out.splitlines() if l.startswith("{")))
         w("headline (bench.py)", sh(run + ["bench.py", "--gpus", str(args.gpus)])[-3000:])
         w("clocks after", sh(clocks))
         w("failed modes", ", ".join(failed) or "none")

@@ -165,6 +165,13 @@ def validation(rank, world):
             lambda: g.all_to_all_4d(ok, out=torch.empty(1, 2, 4 * world, 8).transpose(1, 2)))
     rejects("seq_splits has 0 entries", lambda: g.all_to_all_4d(ok, seq_splits=[], head_splits=[]))
     rejects("does not support torch.vmap", lambda: torch.vmap(lambda t: g.all_to_all_4d(t))(ok.unsqueeze(0)))
+    rejects("transport must be", lambda: g.set_async_transport("dma"), exc=ValueError)
+    # the transport setting is accepted on the CPU executor (where it has nothing to choose) and
+    # the asynchronous call still delivers
+    g.set_async_transport("copy_engine")
+    assert torch.equal(g.all_to_all_4d_async(ok).wait(), g.all_to_all_4d(ok))
+    g.set_async_transport("kernel")
+    dist.barrier()
     # accepted: out= under no_grad with a grad-requiring input
     with torch.no_grad():
         g.all_to_all_4d(ok.clone().requires_grad_(), out=torch.empty(1, 4 * world, 2, 8))
