@@ -194,3 +194,59 @@ def test_rejections(kwargs, fragment):
     mode = kwargs.pop("mode", 0)
     with pytest.raises(RuntimeError, match=fragment):
         plan_debug(1, 4, 0, 3, kwargs["seq"], kwargs["heads"], mode, 2)
+
+
+# ---- property-based: any world size, any split, both modes ---------------------------------------------
+hypothesis = pytest.importorskip("hypothesis")
+from hypothesis import given, settings  # noqa: E402
+from hypothesis import strategies as st  # noqa: E402
+
+
+@st.composite
+def layouts(draw):
+    ws = draw(st.integers(1, 8))
+    seq = draw(st.lists(st.integers(0, 9), min_size=ws, max_size=ws))
+    heads = draw(st.lists(st.integers(0, 5), min_size=ws, max_size=ws))
+    if sum(seq) == 0:
+        seq[draw(st.integers(0, ws - 1))] = 1 + draw(st.integers(0, 5))
+    if sum(heads) == 0:
+        heads[draw(st.integers(0, ws - 1))] = 1 + draw(st.integers(0, 3))
+    return dict(b=draw(st.integers(1, 3)), seq=seq, heads=heads, d=draw(st.sampled_from([4, 8, 16, 32])),
+                mode=draw(st.integers(0, 1)))
+
+
+@settings(max_examples=60, deadline=None)
+@given(layouts())
+def test_any_layout_replays_to_the_permutation(lay):
+    """Random world sizes and splits, empty shards included: replaying every rank's routes over byte
+    windows gives exactly the exchange, the routes of all senders never overlap inside a window,
+    and what lands in a window stays inside the uniform window size."""
+    b, seq, heads, d, mode = lay["b"], lay["seq"], lay["heads"], lay["d"], lay["mode"]
+    plans = check(b, seq, heads, d, mode, np.float32)
+    ws, elem = len(seq), 4
+    wn = plans[0][1]
+    for target in range(ws):
+        covered = np.zeros(wn * elem, dtype=np.uint8)
+        for r in range(ws):
+            for op in routes(plans[r][2]):
+                if op["peer"] != target:
+                    continue
+                for bi in range(op["batches"]):
+                    for row in range(op["rows"]):
+                        do = op["dst_off"] + bi * op["dst_batch"] + row * op["dst_pitch"]
+                        assert do + op["row_bytes"] <= wn * elem
+                        assert not covered[do:do + op["row_bytes"]].any(), "two senders write the same bytes"
+                        covered[do:do + op["row_bytes"]] = 1
+        out_bytes = int(np.prod(list(plans[target][0]))) * elem
+        assert covered[:out_bytes].all() and not covered[out_bytes:].any()
+
+
+@settings(max_examples=40, deadline=None)
+@given(layouts())
+def test_mode_1_undoes_mode_0_for_any_layout(lay):
+    b, seq, heads, d = lay["b"], lay["seq"], lay["heads"], lay["d"]
+    inputs, _ = make_inputs(b, seq, heads, d, 0, np.float32, seed=3)
+    mid, _ = replay(b, seq, heads, d, 0, inputs)
+    back, _ = replay(b, seq, heads, d, 1, [np.ascontiguousarray(m) for m in mid])
+    for r in range(len(seq)):
+        assert np.array_equal(back[r], inputs[r])
