@@ -64,3 +64,19 @@ def test_preflight_refuses_a_machine_without_gpus_and_explains_itself(tmp_path):
     assert r.returncode == 2 and "needs a machine with GPUs" in r.stdout
     h = subprocess.run([sys.executable, script, "--help"], capture_output=True, text=True, timeout=120)
     assert h.returncode == 0 and "exclusive.py" in h.stdout and "doctor" in h.stdout
+
+
+def test_async_overlap_example_runs_on_two_gloo_ranks():
+    """examples/overlap_async.py in its dry-run form: both transports' settings, the staged input,
+    a lent window, every result equal to the synchronous call."""
+    import socket
+
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+                        "--master-addr", "127.0.0.1", "--master-port", str(port),
+                        os.path.join(ROOT, "examples", "overlap_async.py"), "--cpu"],
+                       capture_output=True, text=True, timeout=240, cwd=ROOT)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert r.stdout.count("all equal to the synchronous call") == 2
