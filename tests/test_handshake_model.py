@@ -125,3 +125,82 @@ def test_without_the_opening_wait_a_payload_is_overwritten_unread(world):
 def test_with_completion_announced_before_the_payload_a_reader_sees_stale_data(world):
     found = explore(world, early_publish=True)
     assert found is not None and "finds rank" in found
+
+
+# ---- the pull direction ------------------------------------------------------------------------------
+# The output projection and the gradient pull READ peers' memory: the owner produces its buffer in
+# stream order before the kernel, the opening says "my buffer is complete", a reader loads from a peer
+# once THAT peer has said so, the closing says "I have finished reading everybody's", and only after
+# everyone's closing may the owner's next step overwrite its buffer.
+def pull_program(world, *, closing_wait=True):
+    steps = []
+    for call in range(1, CALLS + 1):
+        steps.append(("produce", None, call))
+        steps += [("announce_open", p, call) for p in range(world)]
+        for p in range(world):
+            steps += [("wait_open", p, call), ("load", p, call)]
+        steps += [("announce_close", p, call) for p in range(world)]
+        if closing_wait:
+            steps.append(("wait_close", None, call))
+    return steps
+
+
+def explore_pull(world, **variant):
+    programs = [pull_program(world, **variant) for _ in range(world)]
+    zeros = tuple(tuple([0] * world) for _ in range(world))
+    # state: program counters, flags[receiver][sender], holds[owner] = call whose data the owner's
+    # buffer holds, loaded[reader][owner] = last call of `owner` that `reader` has loaded
+    start = (tuple([0] * world), zeros, tuple([0] * world), zeros)
+    seen, stack = {start}, [start]
+    while stack:
+        pcs, flags, holds, loaded = stack.pop()
+        if all(pcs[r] == len(programs[r]) for r in range(world)):
+            continue
+        progressed = False
+        for r in range(world):
+            if pcs[r] == len(programs[r]):
+                continue
+            kind, p, call = programs[r][pcs[r]]
+            base = 2 * (call - 1)
+            f = [list(row) for row in flags]
+            h = list(holds)
+            ld = [list(row) for row in loaded]
+            if kind == "produce":
+                late = [q for q in range(world) if loaded[q][r] < call - 1]
+                if late:
+                    return f"rank {r} overwrites its buffer while rank {late[0]} has yet to load call {call - 1}"
+                h[r] = call
+            elif kind == "announce_open":
+                f[p][r] = max(f[p][r], base + 1)
+            elif kind == "announce_close":
+                f[p][r] = max(f[p][r], base + 2)
+            elif kind == "wait_open":
+                if flags[r][p] < base + 1:
+                    continue
+            elif kind == "wait_close":
+                if any(flags[r][q] < base + 2 for q in range(world)):
+                    continue
+            elif kind == "load":
+                if holds[p] != call:
+                    return f"rank {r} loads rank {p}'s buffer in call {call} and finds call {holds[p]}"
+                ld[r][p] = call
+            progressed = True
+            nxt = (tuple(pcs[i] + (1 if i == r else 0) for i in range(world)), tuple(map(tuple, f)), tuple(h),
+                   tuple(map(tuple, ld)))
+            if nxt not in seen:
+                seen.add(nxt)
+                stack.append(nxt)
+        if not progressed:
+            return f"deadlock at program counters {pcs}"
+    return None
+
+
+@pytest.mark.parametrize("world", [1, 2, 3])
+def test_pull_protocol_holds_in_every_interleaving(world):
+    assert explore_pull(world) is None
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_pull_without_the_closing_wait_overwrites_what_a_peer_still_reads(world):
+    found = explore_pull(world, closing_wait=False)
+    assert found is not None and "overwrites its buffer" in found
