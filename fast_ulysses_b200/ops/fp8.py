@@ -91,7 +91,7 @@ def _fused_exchange(group, x, mode, seq_splits, head_splits):
     out_shape, window_numel, sends, _, _ = torch.ops.fast_ulysses_b200.a2a_plan_debug(b, BLOCK, rank, world, list(seq_splits),
                                                                 list(head_splits), mode, 2)
     win_bytes = window_numel // BLOCK * PACKED  # packed bytes of the largest result of any rank
-    cache = group.__dict__.setdefault("_fp8_window", {})
+    cache = group._fp8_window  # one symmetric window per group, grown collectively, dropped by destroy()
     if cache.get("bytes", 0) < win_bytes:  # collective: every rank computes the same size
         buf = group._handle.symm_alloc(win_bytes)
         ptrs = group._handle.symm_ptrs(buf)

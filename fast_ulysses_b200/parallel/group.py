@@ -105,6 +105,7 @@ class UlyssesGroup:
             _, greatest = torch.cuda.Stream.priority_range()
             self._comm_stream = torch.cuda.Stream(device=device, priority=greatest)
         self._destroyed = False
+        self._fp8_window: dict = {}
 
     # ------------------------------------------------------------------------------------------
     def _require_nvlink(self) -> None:
@@ -288,6 +289,7 @@ class UlyssesGroup:
         if self.pg is not None and self.world_size > 1:
             dist.barrier(group=self.pg)
         self._handle.destroy()
+        self._fp8_window = {}  # the fp8 exchange's cached symmetric window (ops/fp8.py) goes with the group
         self._destroyed = True
 
     def __del__(self) -> None:
